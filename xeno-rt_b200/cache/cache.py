@@ -58,7 +58,7 @@ class _KVGroup:
         self.allocator = BlockAllocator(n_blocks)
         shape = (len(entries), max(n_blocks, 1), need.n_kv_heads, BLOCK_TOKENS, need.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = self.k if need.values_in_keys else torch.zeros(shape, dtype=dtype, device=device)
         self.table_host = np.full((max_slots, blocks_per_seq), -1, dtype=np.int32)
         self.table = torch.full((max_slots, blocks_per_seq), -1, dtype=torch.int32, device=device)
         self.dirty: set[int] = set()
@@ -82,7 +82,7 @@ class _KVGroup:
         return max(0, (length - int(self.need.window) + 1) // BLOCK_TOKENS)
 
     def nbytes(self) -> int:
-        return 2 * self.k.numel() * self.k.element_size()
+        return (1 if self.v is self.k else 2) * self.k.numel() * self.k.element_size()
 
 
 def _flatten(need, path=()):

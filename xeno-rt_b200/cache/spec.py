@@ -18,11 +18,14 @@ class KVNeed:
     ``window`` = None keeps every position; a number keeps that many most recent positions
     visible (the storage of a windowed group is its own, so it can be sized and released apart
     from the groups that keep everything); with a window, ``keep_first`` positions at a sequence's start stay
-    visible (and their blocks held) however far the sequence moves."""
+    visible (and their blocks held) however far the sequence moves.  ``values_in_keys``: the layer's values are a
+    part of its key rows (attention in a latent space, where one cached row a token serves as both), so the group
+    has ONE pool and its stores' ``v`` is their ``k``."""
     n_kv_heads: int
     head_dim: int
     window: int | None = None
     keep_first: int = 0
+    values_in_keys: bool = False
 
 
 @dataclass(frozen=True)

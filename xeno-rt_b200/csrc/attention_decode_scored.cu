@@ -1,5 +1,6 @@
 // Attention of single new tokens for layers with score options (ScoreOptions in common.cuh: a window that keeps a
-// sequence's first keys, a tanh cap, a distance slope), bfloat16 cache, 32-bit scores and sums.
+// sequence's first keys, a tanh cap, a distance slope, a sink term in the denominator), bfloat16 cache, 32-bit
+// scores and sums.
 //
 // The keys a token sees are its kept first keys [0, kept) and its window [first, pos]: `total` keys, numbered
 // 0 .. total - 1 in that order.  Grid (tokens, kv heads, splits): a block takes `chunk` of those numbers, its four
@@ -162,6 +163,7 @@ __global__ void __launch_bounds__(DS_WARPS * 32) attention_decode_scored_kernel(
       }
       const int head = kv * group + h0 + g;
       if (a.partial == nullptr) {
+        if (a.opt.sink) sum += expf(a.opt.sink_score - top);
         a.out[((size_t)t * a.n_heads + head) * hd + d] = __float2bfloat16_rn(o / sum);
       } else {
         float* dst = a.partial + (((size_t)t * a.n_heads + head) * a.n_splits + split) * (hd + 2);
@@ -175,7 +177,7 @@ __global__ void __launch_bounds__(DS_WARPS * 32) attention_decode_scored_kernel(
 // The splits of a (token, head), in index order.
 __global__ void attention_decode_scored_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ partial,
                                                      const int* __restrict__ tok_slot, int n_heads, int head_dim,
-                                                     int n_splits) {
+                                                     int n_splits, int sink, float sink_score) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x, head = blockIdx.y;
@@ -191,6 +193,7 @@ __global__ void attention_decode_scored_merge_kernel(__nv_bfloat16* __restrict__
       sum = fmaf(p[head_dim + 1], f, sum);
       o = fmaf(p[d], f, o);
     }
+    if (sink) sum += expf(sink_score - top);
     out[((size_t)t * n_heads + head) * head_dim + d] = __float2bfloat16_rn(o / sum);
   }
 }
@@ -216,8 +219,8 @@ int launch_decode_scored(const DecodeScoredArgs& a, int n_tokens, cudaStream_t s
 XRT_EXPORT int xrt_attention_decode_scored(void* out, float* partial, const void* q, const void* k_pool, const void* v_pool,
                                            const int* tok_slot, const int* tok_pos, const int* block_table, int max_blocks,
                                            int n_tokens, int n_heads, int n_kv_heads, int head_dim, float scale, int window,
-                                           int keep_first, float softcap, float distance_rate, int chunk, int n_splits,
-                                           cudaStream_t stream) {
+                                           int keep_first, float softcap, float distance_rate, int sink, float sink_score,
+                                           int chunk, int n_splits, cudaStream_t stream) {
   if (n_tokens < 0 || n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads || head_dim <= 0 || chunk <= 0 || n_splits <= 0)
     return XRT_ERR_ARGUMENT;
   if (head_dim % 8 || head_dim > 256 || chunk % 32 || n_tokens > 65535 * 32 || n_kv_heads > 65535 || n_splits > 65535 ||
@@ -235,6 +238,8 @@ XRT_EXPORT int xrt_attention_decode_scored(void* out, float* partial, const void
   a.opt.keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
   a.opt.softcap = softcap;
   a.opt.distance_rate = distance_rate;
+  a.opt.sink = sink;
+  a.opt.sink_score = sink_score;
   const int group = n_heads / n_kv_heads;
   const int pairs = head_dim <= 64 ? 1 : (head_dim <= 128 ? 2 : 4);
   int status;
@@ -249,6 +254,6 @@ XRT_EXPORT int xrt_attention_decode_scored(void* out, float* partial, const void
 #undef XRT_DS
   if (status != XRT_OK || n_splits == 1) return status;
   xrt::launch_kernel(xrt::attention_decode_scored_merge_kernel, dim3(n_tokens, n_heads), dim3(head_dim >= 128 ? 128 : 64), 0,
-                     stream, (__nv_bfloat16*)out, (const float*)partial, tok_slot, n_heads, head_dim, n_splits);
+                     stream, (__nv_bfloat16*)out, (const float*)partial, tok_slot, n_heads, head_dim, n_splits, sink, sink_score);
   return xrt::launch_status();
 }

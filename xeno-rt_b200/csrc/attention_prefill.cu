@@ -128,6 +128,8 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
   for (int r = 0; r < 2; ++r) {
     st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
     st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
+    // a sink: one more term of the denominator, exp(sink_score), in the base-2 domain of the running maximum
+    if (opt.sink && st.m[r] != -INFINITY) st.l[r] += exp2f(opt.sink_score * 1.4426950408889634f - st.m[r]);
   }
 #pragma unroll
   for (int dt = 0; dt < D_TILES; ++dt) {
@@ -186,11 +188,14 @@ XRT_EXPORT int xrt_attention_prefill(void* out, const void* q, const void* k_poo
                                      const int* cu_seqlens, const int* seq_slot, const int* seq_start,
                                      const int* block_table, int max_blocks, int n_seqs, int max_new, int n_heads,
                                      int n_kv_heads, int head_dim, float scale, int window, int keep_first,
-                                     float softcap, float distance_rate, cudaStream_t stream) {
+                                     float softcap, float distance_rate, int sink, float sink_score,
+                                     cudaStream_t stream) {
   xrt::ScoreOptions opt;
   opt.keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
   opt.softcap = softcap;
   opt.distance_rate = distance_rate;
+  opt.sink = sink;
+  opt.sink_score = sink_score;
   if (n_seqs < 0 || max_new < 0 || n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return XRT_ERR_ARGUMENT;
   if (head_dim % 16 != 0 || head_dim < 16 || head_dim > 256 || n_seqs > 65535 || (max_new + xrt::PRE_ROWS - 1) / xrt::PRE_ROWS > 65535) return XRT_ERR_UNSUPPORTED;
   if (n_seqs == 0 || max_new == 0) return XRT_OK;

@@ -10,7 +10,8 @@
 // `window` > 0 keeps only keys with pos - j < window (absent in the reference; 0 = all keys).
 // Further options on the scores, all 32-bit and all off at 0 (ScoreOptions in common.cuh): the first `keep_first`
 // keys of a sequence stay visible behind the window; s <- cap * tanh(s / cap); s <- s - slope_h * (pos - j) with
-// slope_h = 2^(-rate (h + 1) / n_heads).
+// slope_h = 2^(-rate (h + 1) / n_heads).  `sink`: the softmax's denominator holds one more term exp(sink_score)
+// that stands for no key and has no value (a head may then give less than a whole average of its values).
 #include "common.cuh"
 
 namespace xrt {
@@ -84,6 +85,7 @@ __global__ void attention_reference_kernel(
   };
   for (int base = 0; base < kept; base += 32) tile_of_keys(base, 0, kept);
   for (int base = (first_key / 32) * 32; base <= pos; base += 32) tile_of_keys(base, first_key, pos + 1);
+  if (opt.sink) running_sum += expf(opt.sink_score - running_max);  // every token sees itself: the maximum is a number
   const float inv = 1.0f / running_sum;
 #pragma unroll
   for (int j = 0; j < MAX_PER_LANE; ++j) {
@@ -99,11 +101,13 @@ XRT_EXPORT int xrt_attention_reference(void* out, const void* q, const void* k_p
                                        const int* tok_slot, const int* tok_pos, const int* block_table,
                                        int max_blocks, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                                        float scale, int window, int keep_first, float softcap, float distance_rate,
-                                       int q_dtype, int cache_dtype, int out_dtype, cudaStream_t stream) {
+                                       int sink, float sink_score, int q_dtype, int cache_dtype, int out_dtype, cudaStream_t stream) {
   xrt::ScoreOptions opt;
   opt.keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
   opt.softcap = softcap;
   opt.distance_rate = distance_rate;
+  opt.sink = sink;
+  opt.sink_score = sink_score;
   if (n_tokens < 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || n_heads % n_kv_heads != 0)
     return XRT_ERR_ARGUMENT;
   if (head_dim > 256) return XRT_ERR_UNSUPPORTED;

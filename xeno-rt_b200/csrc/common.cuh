@@ -62,6 +62,8 @@ struct ScoreOptions {
   int keep_first = 0;
   float softcap = 0.f;
   float distance_rate = 0.f;
+  int sink = 0;            // the softmax's denominator holds one more term exp(sink_score) that has no value
+  float sink_score = 0.f;
 };
 
 __device__ __forceinline__ float to_float(float v) { return v; }

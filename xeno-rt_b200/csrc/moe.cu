@@ -13,9 +13,114 @@
 // For steps of many tokens the rows are sorted by expert instead (xrt_moe_group, xrt_moe_gather), every expert's rows
 // go through the library's matrix products with xrt_moe_activation between them, and xrt_moe_combine writes the same
 // out[choice][token][width].
+// A second kind of expert and of routing, chosen by a number (`act` 1, xrt_moe_route_scores):
+//   expert    W_down gelu(W_up h) with the exact (erf) gelu; w_in then holds one block of ff rows an expert
+//   routing   scores = softmax of the logits over ALL experts; the experts form `groups` equal groups of neighbours, a
+//             group counts by its largest score and only experts of the `keep` best groups can be chosen; the `top`
+//             largest scores among those win, and a chosen expert's weight is its score as it is (no renormalizing)
 #include "common.cuh"
 
 namespace xrt {
+
+constexpr int MOE_ACT_GATED = 0, MOE_ACT_GELU = 1;
+
+__device__ __forceinline__ float gelu_erf(float z) { return 0.5f * z * (1.0f + erff(z * 0.70710678118654752f)); }
+
+// One warp a token.  Lane l holds logits l, l + 32, ...; group_best [warps][groups] in shared memory.
+template <int PER_LANE>
+__global__ void moe_route_scores_kernel(int* __restrict__ ids, float* __restrict__ weights,
+                                        const float* __restrict__ logits, int n_tokens, int n_experts, int top,
+                                        int groups, int keep) {
+  extern __shared__ float group_best[];
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= n_tokens) return;
+  float z[PER_LANE];
+  float top_z = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < PER_LANE; ++i) {
+    const int e = lane + 32 * i;
+    z[i] = e < n_experts ? logits[(size_t)t * n_experts + e] : -INFINITY;
+    top_z = fmaxf(top_z, z[i]);
+  }
+  top_z = warp_max(top_z);
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER_LANE; ++i) {
+    z[i] = lane + 32 * i < n_experts ? expf(z[i] - top_z) : -INFINITY;  // from here on z holds the scores' numerators
+    if (lane + 32 * i < n_experts) sum += z[i];
+  }
+  sum = warp_sum(sum);
+#pragma unroll
+  for (int i = 0; i < PER_LANE; ++i)
+    if (lane + 32 * i < n_experts) z[i] /= sum;
+  if (keep < groups) {
+    float* best_of = group_best + (size_t)warp * groups;
+    const int size = n_experts / groups;
+    for (int g = 0; g < groups; ++g) {
+      float b = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < PER_LANE; ++i) {
+        const int e = lane + 32 * i;
+        if (e < n_experts && e / size == g) b = fmaxf(b, z[i]);
+      }
+      b = warp_max(b);
+      if (lane == 0) best_of[g] = b;
+    }
+    __syncwarp();
+    // the keep best groups, one at a time (the lower number wins a tie); a taken group's entry becomes +inf
+    for (int r = 0; r < keep; ++r) {
+      float b = -INFINITY;
+      int bg = 0x7fffffff;
+      for (int g = lane; g < groups; g += 32) {
+        const float v = best_of[g];
+        if (v != INFINITY && (v > b || (v == b && g < bg) || bg == 0x7fffffff)) { b = v; bg = g; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, b, o);
+        const int other_g = __shfl_xor_sync(0xffffffffu, bg, o);
+        if (other_g != 0x7fffffff && (bg == 0x7fffffff || other > b || (other == b && other_g < bg))) { b = other; bg = other_g; }
+      }
+      __syncwarp();
+      if (lane == 0 && bg != 0x7fffffff) best_of[bg] = INFINITY;
+      __syncwarp();
+    }
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      if (e < n_experts && best_of[e / size] != INFINITY) z[i] = -INFINITY;  // not of a kept group
+    }
+  }
+  for (int c = 0; c < top; ++c) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      if (z[i] > best || (z[i] == best && e < best_e && z[i] > -INFINITY)) { best = z[i]; best_e = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, best, o);
+      const int other_e = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (other > best || (other == best && other_e < best_e)) { best = other; best_e = other_e; }
+    }
+    if (best_e >= n_experts) {  // a row of logits that are no numbers (a padding row's): any expert, no weight
+      best_e = c;
+      best = 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i)
+      if (lane + 32 * i == best_e) z[i] = -INFINITY;  // taken
+    if (lane == 0) {
+      ids[(size_t)t * top + c] = best_e;
+      weights[(size_t)t * top + c] = best;
+    }
+  }
+}
 
 // One warp a token.  Lane l holds logits l, l + 32, ...
 template <int PER_LANE>
@@ -91,7 +196,7 @@ constexpr int MOE_UNITS = 32;
 template <typename TX, typename TW, bool VEC>
 __global__ void __launch_bounds__(256)
 moe_experts_in_kernel(float* __restrict__ act, const TX* __restrict__ h, const TW* __restrict__ w_in,
-                      const int* __restrict__ ids, int width, int ff, int top, float limit, float alpha) {
+                      const int* __restrict__ ids, int width, int ff, int top, float limit, float alpha, int act_kind) {
   extern __shared__ float hs[];  // [width]
   pdl_trigger();
   pdl_wait();
@@ -100,9 +205,17 @@ moe_experts_in_kernel(float* __restrict__ act, const TX* __restrict__ h, const T
   const int e = ids[(size_t)t * top + c];
   for (int k = threadIdx.x; k < width; k += blockDim.x) hs[k] = to_float(h[(size_t)t * width + k]);
   __syncthreads();
+  const int j1 = min(ff, (int)(blockIdx.z + 1) * MOE_UNITS);
+  if (act_kind == MOE_ACT_GELU) {  // one block of ff rows an expert, no gate
+    const TW* only = w_in + (size_t)e * ff * width;
+    for (int j = blockIdx.z * MOE_UNITS + warp; j < j1; j += n_warps) {
+      const float u = row_dot<TW, VEC>(only + (size_t)j * width, hs, width, lane);
+      if (lane == 0) act[((size_t)t * top + c) * ff + j] = gelu_erf(u);
+    }
+    return;
+  }
   const TW* gate = w_in + (size_t)e * 2 * ff * width;
   const TW* up = gate + (size_t)ff * width;
-  const int j1 = min(ff, (int)(blockIdx.z + 1) * MOE_UNITS);
   for (int j = blockIdx.z * MOE_UNITS + warp; j < j1; j += n_warps) {
     float g = row_dot<TW, VEC>(gate + (size_t)j * width, hs, width, lane);
     float u = row_dot<TW, VEC>(up + (size_t)j * width, hs, width, lane);
@@ -183,10 +296,14 @@ __global__ void moe_gather_kernel(TX* __restrict__ out, const TX* __restrict__ h
 // act[r, j] = g * sigmoid(alpha g) * (u + 1) with g = min(gu[r, j], limit), u = clamp(gu[r, ff + j], -limit, limit)
 template <typename TO>
 __global__ void moe_activation_kernel(TO* __restrict__ act, const float* __restrict__ gate_up, size_t total, int ff,
-                                      float limit, float alpha) {
+                                      float limit, float alpha, int act_kind) {
   pdl_trigger();
   pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    if (act_kind == MOE_ACT_GELU) {  // gate_up holds [rows, ff]
+      act[i] = from_float<TO>(gelu_erf(gate_up[i]));
+      continue;
+    }
     const size_t r = i / ff, j = i - r * ff;
     const float g = fminf(gate_up[r * 2 * ff + j], limit);
     const float u = fminf(fmaxf(gate_up[r * 2 * ff + ff + j], -limit), limit);
@@ -229,14 +346,14 @@ XRT_EXPORT int xrt_moe_gather(void* out, const void* h, const int* row_token, in
 }
 
 XRT_EXPORT int xrt_moe_activation(void* act, const float* gate_up, int n_rows, int ff, float limit, float alpha,
-                                  int out_dtype, cudaStream_t stream) {
+                                  int act_kind, int out_dtype, cudaStream_t stream) {
   if (n_rows < 0 || ff <= 0) return XRT_ERR_ARGUMENT;
   if (n_rows == 0) return XRT_OK;
   const size_t total = (size_t)n_rows * ff;
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   XRT_DISPATCH_DTYPE(out_dtype, TO, {
     xrt::launch_kernel(xrt::moe_activation_kernel<TO>, dim3(blocks), dim3(256), 0, stream, (TO*)act, gate_up, total, ff,
-                       limit, alpha);
+                       limit, alpha, act_kind);
   });
   return xrt::launch_status();
 }
@@ -265,11 +382,31 @@ XRT_EXPORT int xrt_moe_route(int* ids, float* weights, const float* logits, cons
   return xrt::launch_status();
 }
 
-// out [top, T, width] float32; h [T, width]; w_in [experts * 2 * ff, width]; w_out [experts * width, ff];
+// The second kind of routing (see the top of the file).  logits [T, experts] float32.
+XRT_EXPORT int xrt_moe_route_scores(int* ids, float* weights, const float* logits, int n_tokens, int n_experts, int top,
+                                    int groups, int keep, cudaStream_t stream) {
+  if (n_tokens < 0 || n_experts <= 0 || top <= 0 || groups <= 0 || keep <= 0 || keep > groups || n_experts % groups)
+    return XRT_ERR_ARGUMENT;
+  if (top > n_experts / groups * keep) return XRT_ERR_ARGUMENT;
+  if (n_experts > 512) return XRT_ERR_UNSUPPORTED;
+  if (n_tokens == 0) return XRT_OK;
+  const dim3 grid((n_tokens + 3) / 4), block(128);
+  const size_t smem = (size_t)4 * groups * sizeof(float);
+#define XRT_ROUTE(PER) xrt::launch_kernel(xrt::moe_route_scores_kernel<PER>, grid, block, smem, stream, ids, weights, logits, n_tokens, n_experts, top, groups, keep)
+  if (n_experts <= 32) XRT_ROUTE(1);
+  else if (n_experts <= 64) XRT_ROUTE(2);
+  else if (n_experts <= 128) XRT_ROUTE(4);
+  else if (n_experts <= 256) XRT_ROUTE(8);
+  else XRT_ROUTE(16);
+#undef XRT_ROUTE
+  return xrt::launch_status();
+}
+
+// out [top, T, width] float32; h [T, width]; w_in [experts * 2 * ff, width] (act 1: [experts * ff, width]); w_out [experts * width, ff];
 // act [T * top, ff] float32 scratch between the two halves.
 XRT_EXPORT int xrt_moe_experts(float* out, float* act, const void* h, const void* w_in, const void* w_out, const int* ids,
                                const float* weights, int n_tokens, int width, int ff, int top, float limit, float alpha,
-                               int h_dtype, int w_dtype, cudaStream_t stream) {
+                               int act_kind, int h_dtype, int w_dtype, cudaStream_t stream) {
   if (n_tokens < 0 || width <= 0 || ff <= 0 || top <= 0) return XRT_ERR_ARGUMENT;
   if (top > 65535 || (ff + xrt::MOE_UNITS - 1) / xrt::MOE_UNITS > 65535 || (width + xrt::MOE_UNITS - 1) / xrt::MOE_UNITS > 65535)
     return XRT_ERR_UNSUPPORTED;
@@ -283,12 +420,12 @@ XRT_EXPORT int xrt_moe_experts(float* out, float* act, const void* h, const void
     XRT_DISPATCH_DTYPE(w_dtype, TW, {
       if (vec) {
         xrt::launch_kernel(xrt::moe_experts_in_kernel<TX, TW, true>, grid_in, dim3(256), (size_t)width * sizeof(float), stream,
-                           act, (const TX*)h, (const TW*)w_in, ids, width, ff, top, limit, alpha);
+                           act, (const TX*)h, (const TW*)w_in, ids, width, ff, top, limit, alpha, act_kind);
         xrt::launch_kernel(xrt::moe_experts_out_kernel<TW, true>, grid_out, dim3(256), (size_t)ff * sizeof(float), stream, out,
                            (const float*)act, (const TW*)w_out, ids, weights, n_tokens, width, ff, top);
       } else {
         xrt::launch_kernel(xrt::moe_experts_in_kernel<TX, TW, false>, grid_in, dim3(256), (size_t)width * sizeof(float), stream,
-                           act, (const TX*)h, (const TW*)w_in, ids, width, ff, top, limit, alpha);
+                           act, (const TX*)h, (const TW*)w_in, ids, width, ff, top, limit, alpha, act_kind);
         xrt::launch_kernel(xrt::moe_experts_out_kernel<TW, false>, grid_out, dim3(256), (size_t)ff * sizeof(float), stream, out,
                            (const float*)act, (const TW*)w_out, ids, weights, n_tokens, width, ff, top);
       }

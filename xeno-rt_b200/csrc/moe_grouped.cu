@@ -8,6 +8,7 @@
 //                   matching up columns and writes act = g * sigmoid(alpha g) * (u + 1), g = min(gate, limit),
 //                   u = clamp(up, -limit, limit), in bfloat16
 //   second product  N = width: 32-bit results
+//   first product of experts without a gate (MODE 2): N = ff, act = gelu(W_up h) with the exact (erf) gelu, bfloat16
 // A row's result does not depend on which other rows share its tile.
 #include "attention_mma.cuh"
 
@@ -25,8 +26,10 @@ struct GroupedArgs {
   float limit, alpha;
 };
 
-template <bool FIRST>
+// MODE 0: second product; 1: first product of gated experts; 2: first product of experts without a gate.
+template <int MODE>
 __global__ void __launch_bounds__(128) moe_grouped_product_kernel(const GroupedArgs g) {
+  constexpr bool FIRST = MODE == 1;
   constexpr int W_TILES = FIRST ? 2 : 1;  // weight tiles a step: gate and up, or one
   extern __shared__ __align__(16) unsigned char smem[];
   pdl_trigger();
@@ -118,6 +121,10 @@ __global__ void __launch_bounds__(128) moe_grouped_product_kernel(const GroupedA
           const float up = fminf(fmaxf(acc[W_TILES - 1][nt][2 * half + i], -g.limit), g.limit);
           ((__nv_bfloat16*)g.out)[(size_t)row * g.ff + col] =
               __float2bfloat16_rn(gate / (1.0f + expf(-g.alpha * gate)) * (up + 1.0f));
+        } else if (MODE == 2) {
+          const float u = acc[0][nt][2 * half + i];
+          ((__nv_bfloat16*)g.out)[(size_t)row * g.n + col] =
+              __float2bfloat16_rn(0.5f * u * (1.0f + erff(u * 0.70710678118654752f)));
         } else {
           ((float*)g.out)[(size_t)row * g.n + col] = acc[0][nt][2 * half + i];
         }
@@ -128,28 +135,30 @@ __global__ void __launch_bounds__(128) moe_grouped_product_kernel(const GroupedA
 
 }  // namespace xrt
 
-// first != 0: act [rows, ff] bfloat16 from a [rows, k] and w [experts, 2 ff, k]; else out [rows, n] float32 from
+// first == 2: act [rows, n] bfloat16 = gelu(a . w^T) from w [experts, n, k] (experts without a gate).
+// first == 1: act [rows, ff] bfloat16 from a [rows, k] and w [experts, 2 ff, k]; else out [rows, n] float32 from
 // a [rows, k] and w [experts, n, k].  offsets [experts + 1] int32 on the device; `rows` is their last entry's bound
 // (the number of (token, choice) pairs).  k must be a multiple of 8 and the bases 16-byte aligned.
 XRT_EXPORT int xrt_moe_grouped_product(void* out, const void* a, const void* w, const int* offsets, int rows, int n_experts,
                                        int n, int k, int ff, float limit, float alpha, int first, cudaStream_t stream) {
-  if (rows < 0 || n_experts <= 0 || n <= 0 || k <= 0 || (first && (ff <= 0 || n != 2 * ff))) return XRT_ERR_ARGUMENT;
+  if (rows < 0 || n_experts <= 0 || n <= 0 || k <= 0 || (first == 1 && (ff <= 0 || n != 2 * ff))) return XRT_ERR_ARGUMENT;
   if (k % 8 || (((uintptr_t)a | (uintptr_t)w) & 15)) return XRT_ERR_UNSUPPORTED;
   if (rows == 0) return XRT_OK;
   xrt::GroupedArgs g;
   g.a = (const __nv_bfloat16*)a; g.w = (const __nv_bfloat16*)w; g.offsets = offsets; g.out = out;
   g.n_experts = n_experts; g.n = n; g.k = k; g.ff = ff; g.limit = limit; g.alpha = alpha;
   const int row_tiles = (rows + xrt::GG_ROWS - 1) / xrt::GG_ROWS + n_experts;  // every expert may leave one tile partly empty
-  const int cols = first ? ff : n;
+  const int cols = first == 1 ? ff : n;
   const int col_tiles = (cols + xrt::GG_COLS - 1) / xrt::GG_COLS;
   if (col_tiles > 65535) return XRT_ERR_UNSUPPORTED;
   const dim3 grid(row_tiles, col_tiles);
-  if (first) {
+  if (first == 1) {
     const size_t smem = 2 * (size_t)(xrt::GG_ROWS + 2 * xrt::GG_COLS) * xrt::GG_STRIDE;
-    xrt::launch_kernel(xrt::moe_grouped_product_kernel<true>, grid, dim3(128), smem, stream, g);
+    xrt::launch_kernel(xrt::moe_grouped_product_kernel<1>, grid, dim3(128), smem, stream, g);
   } else {
     const size_t smem = 2 * (size_t)(xrt::GG_ROWS + xrt::GG_COLS) * xrt::GG_STRIDE;
-    xrt::launch_kernel(xrt::moe_grouped_product_kernel<false>, grid, dim3(128), smem, stream, g);
+    if (first == 2) xrt::launch_kernel(xrt::moe_grouped_product_kernel<2>, grid, dim3(128), smem, stream, g);
+    else xrt::launch_kernel(xrt::moe_grouped_product_kernel<0>, grid, dim3(128), smem, stream, g);
   }
   return xrt::launch_status();
 }

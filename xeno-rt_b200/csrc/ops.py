@@ -36,17 +36,22 @@ _SIGNATURES = {
     "xrt_ssd_scan": [_P, _P, _I, _P, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "xrt_gated_group_norm": [_P, _P, _P, _I, _P, _I, _I, _I, _F, _I, _P],
     "xrt_moe_route": [_P, _P, _P, _P, _I, _I, _I, _P],
-    "xrt_moe_experts": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _F, _I, _I, _P],
+    "xrt_moe_experts": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _F, _I, _I, _I, _P],
     "xrt_relu_squared": [_P, _P, _I, _I, _I, _P],
     "xrt_moe_grouped_product": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _P],
     "xrt_moe_group": [_P, _P, _P, _P, _I, _I, _I, _P],
     "xrt_moe_gather": [_P, _P, _P, _I, _I, _I, _P],
-    "xrt_moe_activation": [_P, _P, _I, _I, _F, _F, _I, _P],
+    "xrt_moe_activation": [_P, _P, _I, _I, _F, _F, _I, _I, _P],
     "xrt_moe_combine": [_P, _P, _P, _P, _I, _I, _I, _P],
     "xrt_embedding_pair": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "xrt_layernorm_affine": [_P, _P, _P, _I, ctypes.c_longlong, _P, _P, _P, _I, _I, _F, _I, _P, _P, _P],
-    "xrt_qkv_heads_write": [_P, _P, _P, _P, _I, _I, _I, _P, _I, _I, _F, _P, _I, _P, _I, _F, _I, _P, _P, _P, _I, _I, _I, _I,
-                            _I, _I, _I, _I, _P],
+    "xrt_qkv_heads_write": [_P, _P, _P, _P, _I, _I, _I, _P, _I, _I, _F, _P, _P, _I, _I, _I, _P, _I, _I,
+                            _P, _I, _P, _I, _F, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "xrt_rmsnorm_add": [_P, _P, ctypes.c_longlong, _I, _P, _P, _I, _I, _F, _I, _I, _P],
+    "xrt_cast_rows": [_P, _P, ctypes.c_longlong, _I, _P],
+    "xrt_latent_prepare": [_P, _P, _P, _I, _I, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "xrt_head_product": [_P, _I, _I, _I, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "xrt_moe_route_scores": [_P, _P, _P, _I, _I, _I, _I, _I, _P],
     "xrt_decay": [_P, _P, _P, _I, _I, _I, _I, _F, _P],
     "xrt_unit_heads": [_P, _I, _I, _I, _I, _F, _I, _F, _P],
     "xrt_head_norm_gate": [_P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P],
@@ -57,7 +62,7 @@ _SIGNATURES = {
     "xrt_rope_table": [_P, _P, _P, _F, _I, _I, _P],
     "xrt_qk_rope_kv_write": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _F, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I,
                              _I, _I, _I, _I, _I, _P],
-    "xrt_attention_reference": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _F, _F, _I, _I, _I, _P],
+    "xrt_attention_reference": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _F, _F, _I, _F, _I, _I, _I, _P],
     "xrt_gemm_reference": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "xrt_gemm_stream": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "xrt_gemm_stream_norm": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P, _I, _P, _P],
@@ -72,8 +77,8 @@ _SIGNATURES = {
     "xrt_attention_decode": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P, _P, _I],
     "xrt_attention_decode_qkv": [_P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _I, _F, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I,
                                  _I, _I, _F, _I, _I, _I, _P, _P, _P, _I],
-    "xrt_attention_decode_scored": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _F, _F, _I, _I, _P],
-    "xrt_attention_prefill": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _F, _F, _P],
+    "xrt_attention_decode_scored": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _F, _F, _I, _F, _I, _I, _P],
+    "xrt_attention_prefill": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _F, _F, _I, _F, _P],
     "xrt_attention_prefill_tcgen05": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P],
     "xrt_fill_normal": [_P, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_double, ctypes.c_double, _I, _P],
     "xrt_sample": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P],
@@ -330,10 +335,11 @@ def qk_rope_kv_write(q_out, k_pool, v_pool, qkv, k_offset: int, v_offset: int, q
 
 def attention_reference(out, q, k_pool, v_pool, tok_slot, tok_pos, block_table, n_heads: int, n_kv_heads: int,
                         head_dim: int, scale: float, window: int = 0, keep_first: int = 0, softcap: float = 0.0,
-                        distance_rate: float = 0.0) -> None:
+                        distance_rate: float = 0.0, sink: float | None = None) -> None:
     """Causal GQA attention over the cache, one warp per (token, head); any dtype.  ``keep_first``: so many first
     keys stay visible behind the window; ``softcap``: s <- cap tanh(s / cap); ``distance_rate`` r: head h's scores
-    lose 2^(-r (h + 1) / heads) for every position between query and key (each 0 = off)."""
+    lose 2^(-r (h + 1) / heads) for every position between query and key (each 0 = off); ``sink`` (None = off): the
+    softmax's denominator holds one more term exp(sink) that has no value."""
     n = q.shape[0]
     if q.shape != (n, n_heads * head_dim) or out.shape != q.shape:
         raise KernelError("attention_reference: shapes do not fit")
@@ -343,8 +349,8 @@ def attention_reference(out, q, k_pool, v_pool, tok_slot, tok_pos, block_table, 
         _ptr(out, "out"), _ptr(q, "q"), _ptr(k_pool, "k_pool"), _ptr(v_pool, "v_pool", k_pool.dtype),
         _ptr(tok_slot, "tok_slot", torch.int32), _ptr(tok_pos, "tok_pos", torch.int32),
         _ptr(block_table, "block_table", torch.int32), block_table.shape[1], n, n_heads, n_kv_heads, head_dim,
-        float(scale), int(window), int(keep_first), float(softcap), float(distance_rate), _code(q.dtype),
-        _code(k_pool.dtype), _code(out.dtype), _stream()),
+        float(scale), int(window), int(keep_first), float(softcap), float(distance_rate),
+        0 if sink is None else 1, float(sink or 0.0), _code(q.dtype), _code(k_pool.dtype), _code(out.dtype), _stream()),
         "attention_reference")
 
 
@@ -679,7 +685,7 @@ def attention_decode_fused_max_splits(head_dim: int, group: int) -> int:
 
 def attention_prefill(out, q, k_pool, v_pool, cu_seqlens, seq_slot, seq_start, block_table, max_new: int,
                       n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int = 0, keep_first: int = 0,
-                      softcap: float = 0.0, distance_rate: float = 0.0) -> None:
+                      softcap: float = 0.0, distance_rate: float = 0.0, sink: float | None = None) -> None:
     """bfloat16 causal attention of sequences laid end to end, each continuing at seq_start.  ``keep_first``,
     ``softcap``, ``distance_rate``: the score options of ``attention_reference``."""
     n = q.shape[0]
@@ -694,12 +700,12 @@ def attention_prefill(out, q, k_pool, v_pool, cu_seqlens, seq_slot, seq_start, b
         _ptr(seq_slot, "seq_slot", torch.int32), _ptr(seq_start, "seq_start", torch.int32),
         _ptr(block_table, "block_table", torch.int32), block_table.shape[1], n_seqs, int(max_new), n_heads,
         n_kv_heads, head_dim, float(scale), int(window), int(keep_first), float(softcap), float(distance_rate),
-        _stream()), "attention_prefill")
+        0 if sink is None else 1, float(sink or 0.0), _stream()), "attention_prefill")
 
 
 def attention_decode_scored(out, q, k_pool, v_pool, tok_slot, tok_pos, block_table, n_heads: int, n_kv_heads: int,
                             head_dim: int, scale: float, window: int, keep_first: int, softcap: float, distance_rate: float,
-                            chunk: int, n_splits: int) -> None:
+                            chunk: int, n_splits: int, sink: float | None = None) -> None:
     """bfloat16 attention of single new tokens with the score options of ``attention_reference``; a token's visible
     keys (kept first keys, then the window) are cut into ``n_splits`` stretches of ``chunk`` keys (a multiple of 32)."""
     n = q.shape[0]
@@ -716,7 +722,8 @@ def attention_decode_scored(out, q, k_pool, v_pool, tok_slot, tok_pos, block_tab
         _ptr(k_pool, "k_pool", torch.bfloat16), _ptr(v_pool, "v_pool", torch.bfloat16),
         _ptr(tok_slot, "tok_slot", torch.int32), _ptr(tok_pos, "tok_pos", torch.int32),
         _ptr(block_table, "block_table", torch.int32), block_table.shape[1], n, n_heads, n_kv_heads, head_dim, float(scale),
-        int(window), int(keep_first), float(softcap), float(distance_rate), int(chunk), int(n_splits), _stream()),
+        int(window), int(keep_first), float(softcap), float(distance_rate), 0 if sink is None else 1, float(sink or 0.0),
+        int(chunk), int(n_splits), _stream()),
         "attention_decode_scored")
 
 
@@ -961,20 +968,33 @@ def moe_route(ids, weights, logits, bias, top: int) -> None:
                                    _stream()), "moe_route")
 
 
-def moe_experts(out, h, w_in, w_out, ids, weights, ff: int, limit: float, alpha: float) -> None:
+MOE_ACTS = {"gated_sigmoid": 0, "gelu": 1}
+
+
+def _moe_act(act: str) -> int:
+    try:
+        return MOE_ACTS[act]
+    except KeyError:
+        raise KernelError(f"experts' activation {act!r} is not one of {sorted(MOE_ACTS)}") from None
+
+
+def moe_experts(out, h, w_in, w_out, ids, weights, ff: int, limit: float = 0.0, alpha: float = 0.0,
+                act: str = "gated_sigmoid") -> None:
     """out[c, t] = weights[t, c] * expert ids[t, c] of h[t]; out float32 [top, T, width]; w_in [experts * 2 * ff,
-    width] (an expert's gate rows, then its up rows), w_out [experts * width, ff]."""
+    width] (an expert's gate rows, then its up rows; with ``act`` "gelu" [experts * ff, width], no gate), w_out
+    [experts * width, ff]."""
     top, n, width = out.shape
+    blocks = 1 if act == "gelu" else 2
     if h.shape != (n, width) or ids.shape != (n, top) or w_in.shape[1] != width or w_out.shape[1] != ff:
         raise KernelError("moe_experts: shapes do not fit")
-    if w_in.shape[0] % (2 * ff) or w_out.shape[0] != w_in.shape[0] // (2 * ff) * width or out.dtype != torch.float32:
+    if w_in.shape[0] % (blocks * ff) or w_out.shape[0] != w_in.shape[0] // (blocks * ff) * width or out.dtype != torch.float32:
         raise KernelError("moe_experts: the experts' matrices do not fit")
-    act = torch.empty((n * top, ff), dtype=torch.float32, device=out.device)  # the hidden units, between the two kernels
+    hidden = torch.empty((n * top, ff), dtype=torch.float32, device=out.device)  # the hidden units, between the two kernels
     add_launches(1)
-    _check(_kernels().xrt_moe_experts(_ptr(out, "out"), _ptr(act, "act"), _ptr(h, "h"), _ptr(w_in, "w_in"), _ptr(w_out, "w_out", w_in.dtype),
+    _check(_kernels().xrt_moe_experts(_ptr(out, "out"), _ptr(hidden, "hidden"), _ptr(h, "h"), _ptr(w_in, "w_in"), _ptr(w_out, "w_out", w_in.dtype),
                                      _ptr(ids, "ids", torch.int32), _ptr(weights, "weights", torch.float32), n, width,
-                                     int(ff), top, float(limit), float(alpha), _code(h.dtype), _code(w_in.dtype),
-                                     _stream()), "moe_experts")
+                                     int(ff), top, float(limit), float(alpha), _moe_act(act), _code(h.dtype),
+                                     _code(w_in.dtype), _stream()), "moe_experts")
 
 
 def moe_group(offsets, pos, row_token, ids, n_experts: int) -> None:
@@ -997,14 +1017,26 @@ def moe_gather(out, h, row_token) -> None:
                                     out.shape[0], out.shape[1], _code(h.dtype), _stream()), "moe_gather")
 
 
-def moe_activation(act, gate_up, limit: float, alpha: float) -> None:
+def moe_activation(act, gate_up, limit: float = 0.0, alpha: float = 0.0, kind: str = "gated_sigmoid") -> None:
     """act = g * sigmoid(alpha g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit); gate_up float32
-    [rows, 2 * ff] (gate columns, then up columns)."""
+    [rows, 2 * ff] (gate columns, then up columns).  ``kind`` "gelu": act = gelu(gate_up) (exact), gate_up [rows, ff]."""
     rows, ff = act.shape
-    if gate_up.shape != (rows, 2 * ff) or gate_up.dtype != torch.float32:
+    if gate_up.shape != (rows, ff if kind == "gelu" else 2 * ff) or gate_up.dtype != torch.float32:
         raise KernelError("moe_activation: shapes do not fit")
     _check(_kernels().xrt_moe_activation(_ptr(act, "act"), _ptr(gate_up, "gate_up"), rows, ff, float(limit), float(alpha),
-                                        _code(act.dtype), _stream()), "moe_activation")
+                                        _moe_act(kind), _code(act.dtype), _stream()), "moe_activation")
+
+
+def moe_route_scores(ids, weights, logits, top: int, groups: int = 1, keep: int = 1) -> None:
+    """Routing by scores: softmax of ``logits`` over all experts; of ``groups`` equal groups of neighbouring experts
+    only the ``keep`` whose best score is largest may be chosen from; ids int32 [T, top] are the ``top`` largest scores
+    among those and weights float32 [T, top] those scores as they are."""
+    n, experts = logits.shape
+    if ids.shape != (n, top) or weights.shape != (n, top) or logits.dtype != torch.float32:
+        raise KernelError("moe_route_scores: shapes do not fit")
+    _check(_kernels().xrt_moe_route_scores(_ptr(ids, "ids", torch.int32), _ptr(weights, "weights", torch.float32),
+                                          _ptr(logits, "logits"), n, experts, int(top), int(groups), int(keep), _stream()),
+           "moe_route_scores")
 
 
 def moe_combine(out, y, pos, weights) -> None:
@@ -1017,19 +1049,22 @@ def moe_combine(out, y, pos, weights) -> None:
                                      _stream()), "moe_combine")
 
 
-def moe_grouped_product(out, a, w, offsets, n_experts: int, ff: int = 0, limit: float = 0.0, alpha: float = 0.0) -> None:
+def moe_grouped_product(out, a, w, offsets, n_experts: int, ff: int = 0, limit: float = 0.0, alpha: float = 0.0,
+                        act: str = "gated_sigmoid") -> None:
     """One launch for all experts' products over rows sorted by expert (bfloat16): with ``ff`` the first product and
-    its activation, out bfloat16 [rows, ff] from a [rows, k] and w [experts * 2 * ff, k]; without, out float32
-    [rows, n] from a [rows, k] and w [experts * n, k].  ``offsets`` int32 [experts + 1] on the device."""
+    its activation, out bfloat16 [rows, ff] from a [rows, k] and w [experts * 2 * ff, k] (``act`` "gelu": w
+    [experts * ff, k], no gate); without, out float32 [rows, n] from a [rows, k] and w [experts * n, k].
+    ``offsets`` int32 [experts + 1] on the device."""
     rows, k = a.shape
-    first = ff > 0
-    n = 2 * ff if first else out.shape[1]
+    first = (2 if act == "gelu" else 1) if ff > 0 else 0
+    n = (2 * ff if first == 1 else ff) if first else out.shape[1]
+    _moe_act(act)
     if w.shape != (n_experts * n, k) or out.shape != (rows, ff if first else n) or offsets.numel() != n_experts + 1:
         raise KernelError("moe_grouped_product: shapes do not fit")
     _check(_kernels().xrt_moe_grouped_product(_ptr(out, "out", torch.bfloat16 if first else torch.float32),
                                              _ptr(a, "a", torch.bfloat16), _ptr(w, "w", torch.bfloat16),
                                              _ptr(offsets, "offsets", torch.int32), rows, int(n_experts), n, k, int(ff),
-                                             float(limit), float(alpha), 1 if first else 0, _stream()),
+                                             float(limit), float(alpha), first, _stream()),
            "moe_grouped_product")
 
 
@@ -1091,13 +1126,27 @@ def layernorm_affine(x, weight, bias, eps: float, out=None, residual=None, rows=
 
 def qkv_heads_write(q_out, k_pool, v_pool, qkv, k_offset: int, v_offset: int, bias, unit_norm: bool, norm_dim: int,
                     eps: float, tok_slot, tok_pos, block_table, n_heads: int, n_kv_heads: int, head_dim: int,
-                    v_keep=None, v_first=None, v_blend: float = 0.0, v_dim: int = 0, write_kv: bool = True) -> None:
+                    v_keep=None, v_first=None, v_blend: float = 0.0, v_dim: int = 0, write_kv: bool = True,
+                    q_norm_w=None, k_norm_w=None, whole_q: int = 0, whole_k: int = 0, cos_sin=None,
+                    pairing: str = "split_half") -> None:
     """``qk_rope_kv_write`` without rotation for layers that add a bias a column of the q/k/v row (float32, laid out as
     the row), divide q and k heads by their root mean square without a weight (over ``norm_dim`` dims where the heads
     are laid out wider), keep the values in 32-bit (``v_keep`` [T, kv heads * v_dim]) and / or cache
     (1 - v_blend) v + v_blend v_first; ``v_dim`` (0: head_dim) is a head's true value size, at which v_keep and
-    v_first hold the heads."""
+    v_first hold the heads.  ``q_norm_w`` / ``k_norm_w`` with ``whole_q`` / ``whole_k`` > 0: an RMSNorm over the
+    whole q (k) projection of a token, all heads at once, one weight a column of the projection as it is laid out, the
+    number being the divisor of the mean of squares; ``cos_sin`` and ``pairing`` as in ``qk_rope_kv_write``."""
     n = qkv.shape[0]
+    if pairing not in ("split_half", "interleaved"):
+        raise KernelError(f"qkv_heads_write: pairing {pairing!r} is not split_half or interleaved")
+    if q_norm_w is not None and q_norm_w.numel() != (n_heads * head_dim if whole_q else head_dim):
+        raise KernelError("qkv_heads_write: the q norm's weight does not fit")
+    if k_norm_w is not None and k_norm_w.numel() != (n_kv_heads * head_dim if whole_k else head_dim):
+        raise KernelError("qkv_heads_write: the k norm's weight does not fit")
+    if q_norm_w is not None and k_norm_w is not None and q_norm_w.dtype != k_norm_w.dtype:
+        raise KernelError("qkv_heads_write: the norm weights must share a dtype")
+    rope_half = 0 if cos_sin is None else cos_sin.shape[1]
+    norm_dtype = q_norm_w.dtype if q_norm_w is not None else torch.float32
     if q_out.shape != (n, n_heads * head_dim) or tok_slot.numel() != n or tok_pos.numel() != n:
         raise KernelError("qkv_heads_write: shapes do not fit")
     if write_kv:
@@ -1120,7 +1169,70 @@ def qkv_heads_write(q_out, k_pool, v_pool, qkv, k_offset: int, v_offset: int, bi
     _check(_kernels().xrt_qkv_heads_write(
         _ptr(q_out, "q_out"), _ptr(k_pool if write_kv else None, "k_pool"), _ptr(v_pool if write_kv else None, "v_pool"),
         _ptr(qkv, "qkv", torch.float32), qkv.shape[1], k_offset, v_offset, _ptr(bias, "bias", torch.float32),
-        1 if unit_norm else 0, int(norm_dim), float(eps), kp, ks, fp, fs, float(v_blend), true_v,
+        1 if unit_norm else 0, int(norm_dim), float(eps), _ptr(q_norm_w, "q_norm_w"), _ptr(k_norm_w, "k_norm_w"),
+        _code(norm_dtype), int(whole_q), int(whole_k), _ptr(cos_sin, "cos_sin", torch.float32), rope_half,
+        1 if pairing == "interleaved" else 0, kp, ks, fp, fs, float(v_blend), true_v,
         _ptr(tok_slot, "tok_slot", torch.int32), _ptr(tok_pos, "tok_pos", torch.int32),
         _ptr(block_table, "block_table", torch.int32), block_table.shape[1], n, n_heads, n_kv_heads, head_dim,
         1 if write_kv else 0, _code(q_out.dtype), _code(cache_dtype), _stream()), "qkv_heads_write")
+
+
+def rmsnorm_add(residual, y, weight, eps: float, copy=None) -> None:
+    """residual += RMSNorm(y) * weight, 32-bit; ``y`` float32 [T, width] or [parts, T, width] (added in index order
+    first); ``copy`` (optional, [T, width] in the compute dtype) receives the new residual as well."""
+    n, width = residual.shape
+    parts = y.shape[0] if y.dim() == 3 else 1
+    if tuple(y.shape[-2:]) != (n, width) or weight.numel() != width or residual.dtype != torch.float32:
+        raise KernelError("rmsnorm_add: shapes do not fit")
+    if copy is not None and tuple(copy.shape) != (n, width):
+        raise KernelError("rmsnorm_add: the copy does not fit")
+    _check(_kernels().xrt_rmsnorm_add(_ptr(residual, "residual"), _ptr(y, "y", torch.float32), n * width, parts,
+                                     _ptr(weight, "weight"), _ptr(copy, "copy"), n, width, float(eps), _code(weight.dtype),
+                                     _code(copy.dtype if copy is not None else torch.float32), _stream()), "rmsnorm_add")
+
+
+def cast_rows(out, x) -> None:
+    """out = x (float32) in out's dtype."""
+    if out.shape != x.shape:
+        raise KernelError("cast_rows: shapes do not fit")
+    _check(_kernels().xrt_cast_rows(_ptr(out, "out"), _ptr(x, "x", torch.float32), x.numel(), _code(out.dtype), _stream()),
+           "cast_rows")
+
+
+def latent_prepare(q_rows, pool, qd, down_offset: int, norm_w, eps: float, cos_sin, tok_slot, tok_pos, block_table,
+                   n_heads: int, dim: int, rot: int, rank: int, head_size: int, write_cache: bool = True,
+                   pairing: str = "interleaved") -> None:
+    """What latent attention does between its first product and attention (csrc/latent.cu): from qd float32
+    [T, heads * (dim + rot) ... | rank + rot at down_offset] the cache row [normed latent | rotated shared key part |
+    zeros] into ``pool`` [blocks, 1, 64, head_size], and every head's rotated query part (and zeros behind it) into
+    columns rank .. head_size of its ``q_rows`` [T, heads * head_size] row."""
+    n = qd.shape[0]
+    if q_rows.shape != (n, n_heads * head_size) or qd.shape[1] < max(n_heads * (dim + rot), down_offset + rank + rot):
+        raise KernelError("latent_prepare: shapes do not fit")
+    if write_cache and tuple(pool.shape[1:]) != (1, 64, head_size):
+        raise KernelError("latent_prepare: the cache pool must be [blocks, 1, 64, head_size]")
+    if norm_w.numel() != rank or (rot and (cos_sin is None or tuple(cos_sin.shape) != (n, rot // 2, 2))):
+        raise KernelError("latent_prepare: the norm weight or the rotation table does not fit")
+    cache_dtype = pool.dtype if write_cache else q_rows.dtype
+    _check(_kernels().xrt_latent_prepare(
+        _ptr(q_rows, "q_rows"), _ptr(pool if write_cache else None, "pool"), _ptr(qd, "qd", torch.float32), qd.shape[1],
+        int(down_offset), _ptr(norm_w, "norm_w"), float(eps), _ptr(cos_sin, "cos_sin", torch.float32),
+        _ptr(tok_slot, "tok_slot", torch.int32), _ptr(tok_pos, "tok_pos", torch.int32),
+        _ptr(block_table, "block_table", torch.int32), block_table.shape[1], n, n_heads, int(dim), int(rot), int(rank),
+        int(head_size), 1 if write_cache else 0, 1 if pairing == "interleaved" else 0, _code(norm_w.dtype),
+        _code(q_rows.dtype), _code(cache_dtype), _stream()), "latent_prepare")
+
+
+def head_product(out, out_head: int, out_off: int, x, x_head: int, x_off: int, w, n_heads: int) -> None:
+    """out[t, head * out_head + out_off + n] = sum_k x[t, head * x_head + x_off + k] * w[head, n, k]; w [heads, n, k];
+    x and out are rows of any width that hold the heads' pieces at those places.  32-bit sums; a float32 x under a
+    bfloat16 w is rounded to bfloat16 first."""
+    heads, n, k = w.shape
+    t = x.shape[0]
+    if heads != n_heads or out.shape[0] != t or x.dim() != 2 or out.dim() != 2 or x.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("head_product: shapes do not fit")
+    if (n_heads - 1) * x_head + x_off + k > x.shape[1] or (n_heads - 1) * out_head + out_off + n > out.shape[1]:
+        raise KernelError("head_product: a head's piece lies outside its row")
+    _check(_kernels().xrt_head_product(_ptr(out, "out"), out.stride(0), int(out_head), int(out_off), _ptr(x, "x"),
+                                      x.stride(0), int(x_head), int(x_off), _ptr(w, "w"), t, n_heads, n, k,
+                                      _code(x.dtype), _code(w.dtype), _code(out.dtype), _stream()), "head_product")

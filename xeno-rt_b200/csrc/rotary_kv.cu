@@ -51,7 +51,13 @@ __global__ void rotation_table_kernel(float2* __restrict__ cos_sin, const int* _
 //   v_first    the cached value is (1 - v_blend) v + v_blend v_first[token], v_first rows of v_first_stride floats
 //   v_dim      the value size of a head in v_keep and v_first, which hold the heads at their true size whatever
 //              size the layer's heads are laid out at (0: head_dim)
+//   whole_q, whole_k   > 0: the RMSNorm of q (of k) runs over the WHOLE projection, all heads of a token at once, with
+//              one weight a column ([heads * head_dim], laid out as the heads are); the number is the divisor of the
+//              mean of squares (the projection's true size, which is smaller than heads * head_dim where the heads
+//              are laid out wider than they are).  Every warp adds up its token's row by itself, in one order.
 struct HeadExtras {
+  int whole_q = 0;
+  int whole_k = 0;
   const float* bias = nullptr;
   int unit_norm = 0;
   int norm_dim = 0;
@@ -110,7 +116,22 @@ __global__ void qk_rope_kv_write_kernel(
   }
   const TN* norm_w = kind == 0 ? q_norm_w : (kind == 1 ? k_norm_w : nullptr);
   const float norm_dim = (float)(ex.norm_dim > 0 ? ex.norm_dim : head_dim);
-  if (norm_w != nullptr) {
+  const int whole = kind == 0 ? ex.whole_q : (kind == 1 ? ex.whole_k : 0);
+  if (norm_w != nullptr && whole > 0) {
+    const float* all = qkv + (size_t)t * row_stride + (kind == 0 ? 0 : k_offset);
+    const int n_all = (kind == 0 ? n_heads : n_kv_heads) * head_dim;
+    float total = 0.f;
+    for (int c = lane; c < n_all; c += 32) {
+      const float a = all[c] + (ex.bias != nullptr ? ex.bias[(kind == 0 ? 0 : k_offset) + c] : 0.f);
+      total = fmaf(a, a, total);
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(total) / (float)whole + eps);
+#pragma unroll
+    for (int j = 0; j < MAX_PER_LANE; ++j) {
+      const int d = lane + 32 * j;
+      if (d < head_dim) v[j] = (v[j] * inv) * to_float(norm_w[head * head_dim + d]);
+    }
+  } else if (norm_w != nullptr) {
     const float inv = 1.0f / sqrtf(warp_sum(sq) / norm_dim + eps);
 #pragma unroll
     for (int j = 0; j < MAX_PER_LANE; ++j) {
@@ -323,10 +344,11 @@ static int qk_rope_kv_write(void* q_out, void* k_pool, void* v_pool, const float
                             const int* tok_pos, const int* block_table, int max_blocks, int n_tokens,
                             int n_heads, int n_kv_heads, int head_dim, int write_kv, int interleaved,
                             int norm_dtype, int q_dtype, int cache_dtype, const xrt::HeadExtras& ex, cudaStream_t stream) {
-  const bool plain = ex.bias == nullptr && !ex.unit_norm && ex.norm_dim == 0 && ex.v_keep == nullptr && ex.v_first == nullptr;
+  const bool plain = ex.bias == nullptr && !ex.unit_norm && ex.norm_dim == 0 && ex.v_keep == nullptr && ex.v_first == nullptr &&
+                     ex.whole_q == 0 && ex.whole_k == 0;
   if (n_tokens < 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0) return XRT_ERR_ARGUMENT;
   if (head_dim > 256 || 2 * rope_half > head_dim) return XRT_ERR_UNSUPPORTED;
-  if ((q_norm_w == nullptr) != (k_norm_w == nullptr)) return XRT_ERR_ARGUMENT;
+  if (write_kv && (q_norm_w == nullptr) != (k_norm_w == nullptr)) return XRT_ERR_ARGUMENT;  // a layer that reads another's keys norms only q
   if (n_tokens == 0) return XRT_OK;
   const bool fast = plain && head_dim == 128 && (rope_half == 0 || (rope_half == 64 && !interleaved)) && row_stride % 4 == 0 && k_offset % 4 == 0 &&
                     v_offset % 4 == 0 &&
@@ -372,10 +394,13 @@ XRT_EXPORT int xrt_qk_rope_kv_write(void* q_out, void* k_pool, void* v_pool, con
                           write_kv, interleaved, norm_dtype, q_dtype, cache_dtype, xrt::HeadExtras(), stream);
 }
 
-// The same with a bias a column, weightless unit norms of q and k, and values that are kept in 32-bit and / or
-// blended with another layer's values of the same tokens before they are cached (see HeadExtras).
+// The same with a bias a column, weightless unit norms of q and k, norms over the whole projection, and values that
+// are kept in 32-bit and / or blended with another layer's values of the same tokens before they are cached (see
+// HeadExtras).
 XRT_EXPORT int xrt_qkv_heads_write(void* q_out, void* k_pool, void* v_pool, const float* qkv, int row_stride,
                                    int k_offset, int v_offset, const float* bias, int unit_norm, int norm_dim, float eps,
+                                   const void* q_norm_w, const void* k_norm_w, int norm_dtype, int whole_q, int whole_k,
+                                   const float* cos_sin, int rope_half, int interleaved,
                                    float* v_keep, int v_keep_stride, const float* v_first, int v_first_stride,
                                    float v_blend, int v_dim, const int* tok_slot, const int* tok_pos, const int* block_table,
                                    int max_blocks, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int write_kv,
@@ -390,7 +415,9 @@ XRT_EXPORT int xrt_qkv_heads_write(void* q_out, void* k_pool, void* v_pool, cons
   ex.v_first_stride = v_first_stride;
   ex.v_blend = v_blend;
   ex.v_dim = v_dim;
-  return qk_rope_kv_write(q_out, k_pool, v_pool, qkv, row_stride, k_offset, v_offset, nullptr, nullptr, eps, nullptr, 0,
-                          tok_slot, tok_pos, block_table, max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, write_kv,
-                          0, XRT_F32, q_dtype, cache_dtype, ex, stream);
+  ex.whole_q = whole_q;
+  ex.whole_k = whole_k;
+  return qk_rope_kv_write(q_out, k_pool, v_pool, qkv, row_stride, k_offset, v_offset, q_norm_w, k_norm_w, eps, cos_sin,
+                          rope_half, tok_slot, tok_pos, block_table, max_blocks, n_tokens, n_heads, n_kv_heads, head_dim,
+                          write_kv, interleaved, norm_dtype, q_dtype, cache_dtype, ex, stream);
 }

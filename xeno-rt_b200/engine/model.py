@@ -61,6 +61,11 @@ class Model:
         order = [firsts[place.layer](self.layers[place.layer]) if firsts[place.layer] and place.before is None else None
                  for place in spec.schedule]
         self._next_layer = order[1:] + [None]
+        # whether the place that runs next reads the residual stream itself (its arrangement says ``reads_stream``):
+        # the part that writes the stream last can then leave the rounded copy that it will read
+        reads = [bool(getattr(self.arrangements[place.layer], "reads_stream", False)) and place.before is None
+                 for place in spec.schedule]
+        self._next_reads_stream = reads[1:] + [False]
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -169,6 +174,7 @@ class Model:
                 x = self.stream_parts[place.before].forward(x, x0, ctx)
             stores = cache.store(i if owns else place.cache_from) or {}
             ctx.shared["next_layer"] = self._next_layer[i]
+            ctx.shared["next_layer_reads_stream"] = self._next_reads_stream[i]
             self.arrangements[place.layer](self.layers[place.layer], x, ctx, stores, owns)
         ctx.pending = ctx.then_norm = None
         if want_rows is None or want_rows.numel() == 0:

@@ -3,5 +3,6 @@
 from . import llama  # registers LlamaForCausalLM and Qwen3ForCausalLM
 from . import givopel  # registers Givopel
 from . import guzuvik  # registers Guzuvik
+from . import zogevik  # registers Zogevik
 
-__all__ = ["llama", "givopel", "guzuvik"]
+__all__ = ["llama", "givopel", "guzuvik", "zogevik"]

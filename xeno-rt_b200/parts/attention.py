@@ -49,7 +49,12 @@ class GroupedQueryAttention:
     square, no weight), ``softcap`` (scores <- cap * tanh(scores / cap)), ``distance_rate`` r (head h's scores lose
     2^(-r (h + 1) / n_heads) for every position between query and key), ``keep_first`` (so many first keys of a
     sequence stay visible behind the window), ``value_blend`` (a name: the first layer of a model that gives this name
-    keeps its values of the step's tokens, every later one caches (1 - b) v + b v_first with its own scalar ``blend``).
+    keeps its values of the step's tokens, every later one caches (1 - b) v + b v_first with its own scalar ``blend``),
+    ``qk_norm`` = "whole" (q and k are RMS-normed over the whole projection, all heads of a token at once, weights
+    ``q_norm`` [n_heads*head_dim] and ``k_norm`` [n_kv_heads*head_dim], before the rotation), ``sink`` (a number s: the
+    softmax's denominator holds one more term exp(s) that has no value, so a head may give less than an average of
+    its values), ``own_kv`` = False (the layer has no k and v products, norms or cache of its own: it is scheduled
+    with ``cache_from`` and reads the keys and values another layer cached, with its own queries, window and scale).
     weights: ``q`` [n_heads*head_dim, width], ``k`` [n_kv_heads*head_dim, width], ``v``
     [n_kv_heads*v_head_dim, width], ``o`` [width, n_heads*v_head_dim], with qk_norm ``q_norm``,
     ``k_norm`` [head_dim], with a gate ``g`` [n_heads*v_head_dim, width].
@@ -71,13 +76,17 @@ class GroupedQueryAttention:
     def fused_weights(cls, params):
         """q, k and v (and the gate's matrix) are one matrix [q rows, k rows, v rows, g rows] for one product."""
         hd, vd, size = cls._sizes(params)
-        if hd != size or vd != size:
+        if hd != size or vd != size or not params.get("own_kv", True):
             return {}  # the part lays the heads out itself
         return {"qkvg": ("q", "k", "v", "g")} if params.get("gate") else {"qkv": ("q", "k", "v")}
 
     @staticmethod
     def _unit_norm(params) -> bool:
         return params.get("qk_norm") == "unit"
+
+    @staticmethod
+    def _whole_norm(params) -> bool:
+        return params.get("qk_norm") == "whole"
 
     @classmethod
     def weight_shapes(cls, params):
@@ -86,8 +95,12 @@ class GroupedQueryAttention:
         shapes = {"q": ((nh * hd, d), "matrix"), "k": ((nkv * hd, d), "matrix"), "v": ((nkv * vd, d), "matrix"),
                   "o": ((d, nh * vd), "matrix")}
         if params.get("qk_norm") and not cls._unit_norm(params):
-            shapes["q_norm"] = ((hd,), "vector")
-            shapes["k_norm"] = ((hd,), "vector")
+            whole = cls._whole_norm(params)
+            shapes["q_norm"] = ((nh * hd if whole else hd,), "vector")
+            shapes["k_norm"] = ((nkv * hd if whole else hd,), "vector")
+        if not params.get("own_kv", True):
+            for role in ("k", "v", "k_norm"):
+                shapes.pop(role, None)
         if params.get("gate"):
             shapes["g"] = ((nh if params["gate"] == "sigmoid_head" else nh * vd, d), "matrix")
         if params.get("bias"):
@@ -108,6 +121,11 @@ class GroupedQueryAttention:
         if self.gate not in (None, "sigmoid", "silu", "sigmoid_head"):
             raise ConfigError(f"attention gate {self.gate!r} is not sigmoid, silu or sigmoid_head")
         self.unit_norm = self._unit_norm(params)
+        self.whole_norm = self._whole_norm(params)
+        self.own_kv = bool(params.get("own_kv", True))
+        self.sink = None if params.get("sink") is None else float(params["sink"])
+        if not self.own_kv and (params.get("bias") or params.get("value_blend")):
+            raise Unsupported("a layer without keys and values of its own cannot have their biases or blend them")
         self.keep_first = int(params.get("keep_first") or 0) if self.window else 0
         self.softcap = float(params.get("softcap") or 0.0)
         self.distance_rate = float(params.get("distance_rate") or 0.0)
@@ -117,7 +135,7 @@ class GroupedQueryAttention:
             raise ConfigError(f"{self.n_heads} heads are not a multiple of {self.n_kv_heads} kv heads")
         if not (16 <= self.head_dim <= 256):
             raise Unsupported(f"head size {max(true_dim, true_vdim)}: the attention kernels take head sizes up to 256")
-        if params.get("qk_norm") and not self.unit_norm and true_dim != self.head_dim:
+        if params.get("qk_norm") and not self.unit_norm and not self.whole_norm and true_dim != self.head_dim:
             raise Unsupported(f"q/k head norms with a head size of {true_dim} (no multiple of 16, or smaller than "
                               f"the value size) are not supported")
         self.q_width = self.n_heads * self.head_dim
@@ -126,9 +144,10 @@ class GroupedQueryAttention:
         self.w_qkv = weights.get("qkvg" if self.gate else "qkv")
         self.w_o = weights["o"]
         if self.w_qkv is None:  # tensors that came one by one, or heads that are laid out at another size
-            pieces = [_pad_rows(weights["q"], self.n_heads, true_dim, self.head_dim),
-                      _pad_rows(weights["k"], self.n_kv_heads, true_dim, self.head_dim),
-                      _pad_rows(weights["v"], self.n_kv_heads, true_vdim, self.head_dim)]
+            pieces = [_pad_rows(weights["q"], self.n_heads, true_dim, self.head_dim)]
+            if self.own_kv:
+                pieces += [_pad_rows(weights["k"], self.n_kv_heads, true_dim, self.head_dim),
+                           _pad_rows(weights["v"], self.n_kv_heads, true_vdim, self.head_dim)]
             if self.gate == "sigmoid_head":
                 pieces.append(weights["g"])
             elif self.gate:
@@ -141,6 +160,10 @@ class GroupedQueryAttention:
         weighted = params.get("qk_norm") and not self.unit_norm
         self.q_norm = weights.get("q_norm") if weighted else None
         self.k_norm = weights.get("k_norm") if weighted else None
+        if self.whole_norm and true_dim != self.head_dim:  # one weight a column of the projection as it is laid out
+            self.q_norm = _pad_rows(self.q_norm.reshape(-1, 1), self.n_heads, true_dim, self.head_dim).reshape(-1)
+            if self.k_norm is not None:
+                self.k_norm = _pad_rows(self.k_norm.reshape(-1, 1), self.n_kv_heads, true_dim, self.head_dim).reshape(-1)
         # one 32-bit bias a column of the q/k/v product's row, laid out as the row is (nothing for the gate's columns)
         self.bias = None
         if params.get("bias"):
@@ -152,13 +175,12 @@ class GroupedQueryAttention:
         self.blend = float(weights["blend"].to(torch.float32).reshape(-1)[0]) if self.value_blend else 0.0
         # what the rotation kernel and the kernels that fold it in do not do: these layers prepare their heads with
         # ops.qkv_heads_write and attend with the kernels that take the score options
-        self.plain_heads = self.bias is None and not self.unit_norm and not self.value_blend and true_dim == self.head_dim
-        self.plain_scores = not (self.keep_first or self.softcap or self.distance_rate)
+        self.plain_heads = (self.bias is None and not self.unit_norm and not self.whole_norm and not self.value_blend
+                            and true_dim == self.head_dim)
+        self.plain_scores = not (self.keep_first or self.softcap or self.distance_rate) and self.sink is None
         position = params.get("position") or {"kind": "none", "params": {}}
         self.position = part_class("position", position["kind"])(position.get("params", {}), {}, dtype, device)
         rope_dim = getattr(self.position, "rope_dim", 0)
-        if rope_dim and (self.bias is not None or self.unit_norm or self.value_blend):
-            raise Unsupported("a rotation together with biases, unit head norms or blended values is not supported")
         if rope_dim > true_dim:
             raise ConfigError(f"rope_dim {rope_dim} exceeds the head size {true_dim}")
         self.scale = float(params["scale"]) if params.get("scale") is not None else 1.0 / math.sqrt(true_dim)
@@ -227,7 +249,10 @@ class GroupedQueryAttention:
                                     self.unit_norm, self.true_dim, self.eps, ctx.tok_slot, ctx.tok_pos, store.block_table,
                                     self.n_heads, self.n_kv_heads, self.head_dim, v_keep=v_keep, v_first=v_first,
                                     v_blend=self.blend if v_first is not None else 0.0, v_dim=self.true_vdim,
-                                    write_kv=owns_cache)
+                                    write_kv=owns_cache, q_norm_w=self.q_norm, k_norm_w=self.k_norm if owns_cache else None,
+                                    whole_q=self.n_heads * self.true_dim if self.whole_norm else 0,
+                                    whole_k=self.n_kv_heads * self.true_dim if self.whole_norm else 0,
+                                    cos_sin=cos_sin, pairing=pairing)
             self.attend(attended, q, ctx, store)
         if self.gate == "sigmoid_head":
             ops.gate_mul(attended, projected[:, self.gate_offset:], "sigmoid", group=self.head_dim)
@@ -238,7 +263,7 @@ class GroupedQueryAttention:
     def attend(self, out, q, ctx, store):
         window = int(self.window) if self.window else 0
         options = {} if self.plain_scores else {"keep_first": self.keep_first, "softcap": self.softcap,
-                                                "distance_rate": self.distance_rate}
+                                                "distance_rate": self.distance_rate, "sink": self.sink}
         if self.dtype is DType.BF16:
             from . import attention_bf16
             if attention_bf16.run(out, q, ctx, store, self.n_heads, self.n_kv_heads, self.head_dim, self.scale,

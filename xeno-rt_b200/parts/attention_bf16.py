@@ -101,22 +101,24 @@ def scored_decode_split(n_tokens: int, n_kv_heads: int, context: int, window: in
 
 
 def run(out, q, ctx, store, n_heads, n_kv_heads, head_dim, scale, window, keep_first=0, softcap=0.0,
-        distance_rate=0.0) -> bool:
+        distance_rate=0.0, sink=None) -> bool:
     if n_heads // n_kv_heads > 16:
         return False
-    scored = bool(keep_first or softcap or distance_rate)  # the layer's score options: kernels that take them only
+    # the layer's score options: kernels that take them only
+    scored = bool(keep_first or softcap or distance_rate) or sink is not None
     if scored and ctx.all_single and head_dim % 8 == 0 and n_kv_heads <= 65535:
         chunk, n_splits = scored_decode_split(ctx.n_tokens, n_kv_heads, context_bucket(ctx.max_context), window,
                                               keep_first, ops.device_state(q.device)[2])
         ops.attention_decode_scored(out, q, store.k, store.v, ctx.tok_slot, ctx.tok_pos, store.block_table, n_heads,
-                                    n_kv_heads, head_dim, scale, window, keep_first, softcap, distance_rate, chunk, n_splits)
+                                    n_kv_heads, head_dim, scale, window, keep_first, softcap, distance_rate, chunk, n_splits,
+                                    sink=sink)
         return True
     if scored:
         if head_dim % 16 or ctx.n_seqs > 65535 or n_heads > 65535:
             return False
         ops.attention_prefill(out, q, store.k, store.v, ctx.cu_seqlens, ctx.seq_slot, ctx.seq_start,
                               store.block_table, ctx.max_new, n_heads, n_kv_heads, head_dim, scale, window,
-                              keep_first, softcap, distance_rate)
+                              keep_first, softcap, distance_rate, sink=sink)
         return True
     if ctx.all_single and ctx.n_tokens <= 65535:
         chunk, n_splits, clusters = _decode_split_of(ctx, n_kv_heads, q.device, window)

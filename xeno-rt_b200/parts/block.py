@@ -1,6 +1,9 @@
 """Arrangements: how the parts of one layer are put together around the residual stream."""
 from __future__ import annotations
 
+import torch
+
+from ..csrc import ops
 from .registry import register_part
 
 
@@ -91,6 +94,45 @@ def sandwich_residual(parts: LayerParts, x, ctx, stores, owns_cache: bool) -> No
         h = parts.ffn_post.add_into(x, parts.ffn.apply(h, ctx), then=following)
     if h is not None:
         ctx.pending = ReadyNorm(following, h)
+
+
+def postnorm_residual(parts: LayerParts, x, ctx, stores, owns_cache: bool) -> None:
+    """x += norm(mixer(x)); x += norm(feed_forward(x)): the sublayers read the residual stream itself and only what
+    they give is normed.  The layer's parts are ``mixer``, ``mixer_post`` and, if it has a feed-forward, ``ffn`` and
+    ``ffn_post``.  The mixer hands its result back (``mix``), the feed-forward too (``apply``: [T, width] or [parts, T,
+    width] float32), and the norm after adds into the 32-bit stream (``add_into``).  In a 16-bit compute dtype the
+    sublayers' products read a rounded copy of the stream, which the adding norm writes in the same pass (left in
+    ``ctx.pending`` for the layer that runs next); only a layer that finds none there rounds the stream itself."""
+    ready, ctx.pending, ctx.then_norm = ctx.pending, None, None
+    rounds = parts.mixer_post.out_dtype != torch.float32
+    if not rounds:
+        h = x
+    elif isinstance(ready, StreamCopy) and ready.of is x:
+        h = ready.value
+    else:
+        h = torch.empty(x.shape, dtype=parts.mixer_post.out_dtype, device=x.device)
+        ops.cast_rows(h, x)
+    has_ffn = "ffn" in parts
+    follows = ctx.shared.get("next_layer_reads_stream", False)
+    h = parts.mixer_post.add_into(x, parts.mixer.mix(h, ctx, stores.get("mixer"), owns_cache),
+                                  copy=rounds and (has_ffn or follows))
+    ctx.then_norm = ctx.pending = None
+    if has_ffn:
+        h = parts.ffn_post.add_into(x, parts.ffn.apply(x if not rounds else h, ctx), copy=rounds and follows)
+    if rounds and h is not None:
+        ctx.pending = StreamCopy(x, h)
+
+
+class StreamCopy:
+    """The residual stream ``of`` rounded to the compute dtype by the part that wrote it last."""
+
+    def __init__(self, of, value):
+        self.of, self.value = of, value
+        self.norm = None  # it stands for no norm: arrangements that look for a prepared norm pass it by
+
+
+postnorm_residual.reads_stream = True
+register_part("arrangement", "postnorm_residual", postnorm_residual)
 
 
 class ReadyNorm:

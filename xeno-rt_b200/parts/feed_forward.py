@@ -5,7 +5,7 @@ from __future__ import annotations
 
 import torch
 
-from ..core import DType, torch_dtype
+from ..core import ConfigError, DType, torch_dtype
 from ..csrc import ops
 from .linear import linear
 from .registry import register_part
@@ -96,30 +96,60 @@ class RoutedExperts:
     params: ``width``, ``inner`` (an expert's), ``experts``, ``top``, ``limit``, ``alpha``.
     weights: ``router`` [experts, width], ``router_bias`` [experts], and for expert i ``gate<i>``, ``up<i>``
     [inner, width], ``down<i>`` [width, inner]; they are kept as two buffers, [experts * 2 * inner, width] (an expert's
-    gate rows, then its up rows) and [experts * width, inner]."""
+    gate rows, then its up rows) and [experts * width, inner].
+
+    Other kinds of expert and of routing, by parameter:
+    ``activation`` = "gelu": an expert is W_down gelu(W_up h) with the exact (erf) gelu and has no gate (no ``gate<i>``,
+    ``limit`` or ``alpha``; the first buffer is [experts * inner, width]).
+    ``routing`` = "scores": the weights are the softmax of the logits over ALL experts, as they are (not renormalized
+    over the chosen); with ``groups`` (a number of equal groups of neighbouring experts) and ``keep_groups``, only
+    experts of the ``keep_groups`` groups whose best score is largest can be chosen.  ``router_bias`` = False: the
+    router has no bias tensor."""
 
     graph_safe = True
+
+    @staticmethod
+    def _gated(params) -> bool:
+        return params.get("activation", "gated_sigmoid") != "gelu"
 
     @classmethod
     def fused_weights(cls, params):
         n = int(params["experts"])
-        return {"experts_in": tuple(r for i in range(n) for r in (f"gate{i}", f"up{i}")),
+        first = (lambda i: (f"gate{i}", f"up{i}")) if cls._gated(params) else (lambda i: (f"up{i}",))
+        return {"experts_in": tuple(r for i in range(n) for r in first(i)),
                 "experts_out": tuple(f"down{i}" for i in range(n))}
 
     @classmethod
     def weight_shapes(cls, params):
         d, f, n = params["width"], params["inner"], int(params["experts"])
-        shapes = {"router": ((n, d), "matrix"), "router_bias": ((n,), "vector")}
+        shapes = {"router": ((n, d), "matrix")}
+        if params.get("router_bias", True):
+            shapes["router_bias"] = ((n,), "vector")
         for i in range(n):
-            shapes.update({f"gate{i}": ((f, d), "matrix"), f"up{i}": ((f, d), "matrix"), f"down{i}": ((d, f), "matrix")})
+            shapes.update({f"up{i}": ((f, d), "matrix"), f"down{i}": ((d, f), "matrix")})
+            if cls._gated(params):
+                shapes[f"gate{i}"] = ((f, d), "matrix")
         return shapes
 
     def __init__(self, params, weights, dtype: DType, device):
         self.width, self.inner = int(params["width"]), int(params["inner"])
         self.experts, self.top = int(params["experts"]), int(params["top"])
-        self.limit, self.alpha = float(params["limit"]), float(params["alpha"])
+        self.act = "gated_sigmoid" if self._gated(params) else "gelu"
+        self.limit, self.alpha = float(params.get("limit") or 0.0), float(params.get("alpha") or 0.0)
+        self.routing = params.get("routing", "top_softmax")
+        if self.routing not in ("top_softmax", "scores"):
+            raise ConfigError(f"routing {self.routing!r} is not top_softmax or scores")
+        self.groups, self.keep_groups = int(params.get("groups") or 1), int(params.get("keep_groups") or 1)
+        if self.routing == "scores":
+            if self.experts % self.groups or not 1 <= self.keep_groups <= self.groups:
+                raise ConfigError(f"{self.experts} experts do not form {self.groups} equal groups of which "
+                                  f"{self.keep_groups} are kept")
+            if self.top > self.experts // self.groups * self.keep_groups:
+                raise ConfigError(f"top {self.top} exceeds the experts of {self.keep_groups} kept groups")
         self.w_router = weights["router"]
-        self.router_bias = weights["router_bias"].to(torch.float32).contiguous()
+        self.router_bias = None
+        if params.get("router_bias", True):
+            self.router_bias = weights["router_bias"].to(torch.float32).contiguous()
         fused = self.fused_weights(params)
         self.w_in = weights.get("experts_in")
         if self.w_in is None:
@@ -134,7 +164,12 @@ class RoutedExperts:
         logits = linear(h, self.w_router, out_dtype=torch.float32)
         ids = torch.empty((n, self.top), dtype=torch.int32, device=h.device)
         weights = torch.empty((n, self.top), dtype=torch.float32, device=h.device)
-        ops.moe_route(ids, weights, logits, self.router_bias, self.top)
+        if self.routing == "scores":
+            if self.router_bias is not None:
+                logits += self.router_bias
+            ops.moe_route_scores(ids, weights, logits, self.top, self.groups, self.keep_groups)
+        else:
+            ops.moe_route(ids, weights, logits, self.router_bias, self.top)
         return ids, weights
 
     GROUPED_FROM = 4  # (token, choice) pairs an expert from which a step's rows are sorted by expert
@@ -153,7 +188,7 @@ class RoutedExperts:
         one_launch = h.dtype == torch.bfloat16 and self.width % 8 == 0 and self.inner % 8 == 0
         fixed_shapes = getattr(ctx, "captured", False) or ctx.all_single  # no read-back inside such a step
         if pairs < self.GROUPED_FROM * self.experts or (fixed_shapes and not one_launch):
-            ops.moe_experts(out, h, self.w_in, self.w_out, ids, weights, self.inner, self.limit, self.alpha)
+            ops.moe_experts(out, h, self.w_in, self.w_out, ids, weights, self.inner, self.limit, self.alpha, act=self.act)
             return out
         offsets = torch.empty((self.experts + 1,), dtype=torch.int32, device=h.device)
         pos = torch.empty((pairs,), dtype=torch.int32, device=h.device)
@@ -165,7 +200,8 @@ class RoutedExperts:
             # all experts in one launch a product: the blocks find their expert from the offsets on the device
             act = torch.empty((pairs, self.inner), dtype=h.dtype, device=h.device)
             y = torch.empty((pairs, self.width), dtype=torch.float32, device=h.device)
-            ops.moe_grouped_product(act, rows, self.w_in, offsets, self.experts, self.inner, self.limit, self.alpha)
+            ops.moe_grouped_product(act, rows, self.w_in, offsets, self.experts, self.inner, self.limit, self.alpha,
+                                    act=self.act)
             ops.moe_grouped_product(y, act, self.w_out, offsets, self.experts)
         else:
             bounds = offsets.tolist()  # here the host waits for the device: how many rows each expert has
@@ -174,9 +210,9 @@ class RoutedExperts:
             for e in range(self.experts):
                 lo, hi = bounds[e], bounds[e + 1]
                 if hi > lo:
-                    gate_up = linear(rows[lo:hi], self.w_in[e * 2 * self.inner:(e + 1) * 2 * self.inner],
-                                     out_dtype=torch.float32)
-                    ops.moe_activation(act[lo:hi], gate_up, self.limit, self.alpha)
+                    first = (2 if self.act == "gated_sigmoid" else 1) * self.inner  # rows of an expert in the first buffer
+                    gate_up = linear(rows[lo:hi], self.w_in[e * first:(e + 1) * first], out_dtype=torch.float32)
+                    ops.moe_activation(act[lo:hi], gate_up, self.limit, self.alpha, kind=self.act)
                     linear(act[lo:hi], self.w_out[e * self.width:(e + 1) * self.width], accumulate_into=y[lo:hi])
         ops.moe_combine(out, y, pos, weights)
         return out

@@ -59,6 +59,24 @@ class RMSNorm:
         ops.rmsnorm(out, x, self.weight, self.eps, rows)
         return out
 
+    def forward_f32(self, x):
+        """The norm of the float32 rows ``x`` as float32 (a norm on the residual stream itself)."""
+        out = torch.empty((x.shape[0], self.width), dtype=torch.float32, device=x.device)
+        ops.rmsnorm(out, x, self.weight, self.eps, None)
+        return out
+
+    def add_into(self, residual, y, copy: bool = False):
+        """residual += norm(y), 32-bit (a norm that follows a sublayer).  ``y`` float32 [T, width] or [parts, T,
+        width], whose parts are added in index order first.  ``copy``: the new residual is also returned in the
+        compute dtype, written in the same pass (what the next sublayer's products read), else None."""
+        if y.dim() == 3 and y.shape[0] == 1:
+            y = y[0]
+        out = None
+        if copy:
+            out = torch.empty(residual.shape, dtype=self.out_dtype, device=residual.device)
+        ops.rmsnorm_add(residual, y, self.weight, self.eps, copy=out)
+        return out
+
 
 class LayerNorm:
     """y = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * w (+ b with ``bias``), statistics in 32-bit.

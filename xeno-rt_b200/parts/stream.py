@@ -31,4 +31,26 @@ class MixWithEmbedding:
         return linear(both, self.weight, out_dtype=torch.float32)
 
 
+class NormedStream:
+    """x <- RMSNorm(x) * w in 32-bit: a norm on the residual stream itself (right after the embedding, say).
+    params: ``width``, ``eps``.  weights: ``weight`` [width]."""
+
+    graph_safe = True
+
+    @classmethod
+    def weight_shapes(cls, params):
+        return {"weight": ((params["width"],), "vector")}
+
+    def __init__(self, params, weights, dtype, device):
+        self.width = int(params["width"])
+        self.eps = float(params["eps"])
+        self.weight = weights["weight"]
+
+    def forward(self, x, x0, ctx):
+        out = torch.empty_like(x)
+        ops.rmsnorm(out, x, self.weight, self.eps, None)
+        return out
+
+
 register_part("stream", "mix_with_embedding", MixWithEmbedding)
+register_part("stream", "rmsnorm", NormedStream)
