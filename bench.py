@@ -335,7 +335,31 @@ def guzuvik_config(width: int, heads: int, kv_heads: int, head_dim: int, inner: 
             "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in (pattern[i % 4] for i in range(layers))]}
 
 
-DESIGN_CONFIGS = {"givopel": givopel_config, "guzuvik": guzuvik_config}
+def zogevik_config(width: int, heads: int, kv_heads: int, head_dim: int, inner: int, layers: int, vocab: int) -> dict:
+    """A Zogevik model at the sizes of a dense decoder of that width: layers go attention, latent attention, attention
+    that reads the first layer's keys and values, latent attention, and again; every layer with 16 experts of
+    ``inner`` / 8 units in 4 groups of which 2 are kept and a token uses 2.  Attention has ``heads`` x ``head_dim`` with
+    ``kv_heads`` kv heads, a rotation over half of the head and a window of 1,024 keys; latent attention has ``heads``
+    heads of ``head_dim`` plain and 64 rotated dimensions over a latent of 192 (a cached row of 256), window 1,024."""
+    rot = {"dims": head_dim // 2, "base": 500000.0}
+    attn = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
+            "rot": rot, "mask": {"size": 1024}}
+    latent = {"heads": heads, "dim": head_dim, "rot_dim": 64, "vdim": head_dim, "kv_rank": 192,
+              "scale": (head_dim + 64) ** -0.5, "rot": {"dims": 64, "base": 1000000.0}, "mask": {"size": 1024}}
+    moe = {"kind": "moe", "expert": {"ff": inner // 8}, "router": {"experts": 16, "top": 2, "groups": {"count": 4, "keep": 2}}}
+    out = []
+    for i in range(layers):
+        if i % 4 == 2:
+            out.append({"type": "attention", "mixer": dict(attn, kv_from=i - 2), "mlp": moe})
+        else:
+            out.append({"type": "attention" if i % 2 == 0 else "latent_attention", "mixer": attn if i % 2 == 0 else latent,
+                        "mlp": moe})
+    return {"architecture": "Zogevik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": out}
+
+
+DESIGN_CONFIGS = {"givopel": givopel_config, "guzuvik": guzuvik_config, "zogevik": zogevik_config}
+# the library's model that is closest to a design, timed beside it at equal sizes (besides the dense decoder)
+DESIGN_NEIGHBOUR = {"zogevik": "guzuvik"}
 
 DESIGN_SIZES = {
     # name: (width, heads, kv heads, head size, feed-forward width, vocabulary)
@@ -381,8 +405,11 @@ def run_design(args) -> int:
                      num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=head_dim,
                      max_position_embeddings=max(8192, args.context, args.prefill_tokens))
         row = {}
-        for label, cfg in ((args.design, DESIGN_CONFIGS[args.design](width, heads, kv_heads, head_dim, inner, layers, vocab)),
-                           ("llama", dense)):
+        arms = [(args.design, DESIGN_CONFIGS[args.design](width, heads, kv_heads, head_dim, inner, layers, vocab))]
+        if args.design in DESIGN_NEIGHBOUR:
+            near = DESIGN_NEIGHBOUR[args.design]
+            arms.append((near, DESIGN_CONFIGS[near](width, heads, kv_heads, head_dim, inner, layers, vocab)))
+        for label, cfg in arms + [("llama", dense)]:
             model = Model.random(cfg, seed=0, dtype="bfloat16", device="cuda:0")
             prefill_ms = time_prefill(model, args.prefill_tokens, iters=5, warmup=3)
             decode = time_decode(model, args.batch, args.context, args.steps, max(3, args.warmup))
@@ -586,7 +613,7 @@ def main() -> int:
     parser.add_argument("--only", default="all", choices=["all", "decode", "prefill", "attention"],
                         help="a short run of one part, for profiling; prints its own small JSON line "
                              "(attention: the decode attention kernel alone)")
-    parser.add_argument("--design", default="", choices=["", "givopel", "guzuvik"],
+    parser.add_argument("--design", default="", choices=["", *sorted(DESIGN_CONFIGS)],
                         help="instead of the headline line: prompt and decode throughput of that design at sizes that "
                              "resemble a real model's layers, beside the dense decoder at equal sizes (--layers, default 8; "
                              "--prefill-tokens, --batch, --context, --steps as for the headline run)")

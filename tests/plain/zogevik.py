@@ -148,21 +148,23 @@ def choose(scores, top: int, groups: int, keep: int):
 
 
 def route_margins(h, router, top, groups, keep):
-    """For every token, how close its routing was to another outcome, in score: the smallest of (a) the last chosen
-    score minus the best allowed one that was not chosen, (b) the last kept group's best minus the best dropped
-    group's best.  inf where nothing else could have happened."""
+    """For every token, how close its routing was to another outcome, as a difference of log scores (which is the
+    difference of the router's logits): the smallest of (a) the last chosen score against the best allowed one that
+    was not chosen, (b) the last kept group's best against the best dropped group's best.  inf where nothing else
+    could have happened."""
     s = router_scores(h, router)
     n = s.shape[1]
     size = n // groups
     out = []
     for row in s:
-        best = sorted((max(row[g * size:(g + 1) * size]) for g in range(groups)), reverse=True)
+        logs = np.log(np.maximum(row, 1e-300))
+        best = sorted((max(logs[g * size:(g + 1) * size]) for g in range(groups)), reverse=True)
         margin = best[keep - 1] - best[keep] if keep < groups else math.inf
         chosen = choose(row, top, groups, keep)
         kept = {e // size for e in chosen} | set(sorted(range(groups), key=lambda g: (-max(row[g * size:(g + 1) * size]), g))[:keep])
-        rest = [row[e] for e in range(n) if e // size in kept and e not in chosen]
+        rest = [logs[e] for e in range(n) if e // size in kept and e not in chosen]
         if rest:
-            margin = min(margin, row[chosen[-1]] - max(rest))
+            margin = min(margin, logs[chosen[-1]] - max(rest))
         out.append(margin)
     return np.array(out)
 

@@ -110,19 +110,28 @@ XRT_EXPORT int xrt_attention_reference(void* out, const void* q, const void* k_p
   opt.sink_score = sink_score;
   if (n_tokens < 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || n_heads % n_kv_heads != 0)
     return XRT_ERR_ARGUMENT;
-  if (head_dim > 256) return XRT_ERR_UNSUPPORTED;
+  if (head_dim > 1024) return XRT_ERR_UNSUPPORTED;
   if (n_tokens == 0) return XRT_OK;
   const int warps = 4;
   dim3 grid(n_tokens, (n_heads + warps - 1) / warps);
   const size_t smem = (size_t)warps * head_dim * sizeof(float);
-  XRT_DISPATCH_DTYPE(q_dtype, TQ, {
-    XRT_DISPATCH_DTYPE(cache_dtype, TC, {
-      XRT_DISPATCH_DTYPE(out_dtype, TO, {
-        xrt::attention_reference_kernel<TQ, TC, TO, 8><<<grid, warps * 32, smem, stream>>>(
-            (TO*)out, (const TQ*)q, (const TC*)k_pool, (const TC*)v_pool, tok_slot, tok_pos, block_table,
-            max_blocks, n_heads, n_kv_heads, head_dim, scale, window, opt);
-      });
-    });
-  });
+  // a lane holds head_dim / 32 sums: 8 for the heads the other kernels take too, 32 for rows up to 1,024 wide (the
+  // cached rows of a large latent space)
+#define XRT_REFERENCE_LAUNCH(PER_LANE)                                                                          \
+  XRT_DISPATCH_DTYPE(q_dtype, TQ, {                                                                             \
+    XRT_DISPATCH_DTYPE(cache_dtype, TC, {                                                                       \
+      XRT_DISPATCH_DTYPE(out_dtype, TO, {                                                                       \
+        xrt::attention_reference_kernel<TQ, TC, TO, PER_LANE><<<grid, warps * 32, smem, stream>>>(              \
+            (TO*)out, (const TQ*)q, (const TC*)k_pool, (const TC*)v_pool, tok_slot, tok_pos, block_table,       \
+            max_blocks, n_heads, n_kv_heads, head_dim, scale, window, opt);                                     \
+      });                                                                                                       \
+    });                                                                                                         \
+  })
+  if (head_dim <= 256) {
+    XRT_REFERENCE_LAUNCH(8);
+  } else {
+    XRT_REFERENCE_LAUNCH(32);
+  }
+#undef XRT_REFERENCE_LAUNCH
   return xrt::launch_status();
 }

@@ -1201,13 +1201,16 @@ def cast_rows(out, x) -> None:
 
 def latent_prepare(q_rows, pool, qd, down_offset: int, norm_w, eps: float, cos_sin, tok_slot, tok_pos, block_table,
                    n_heads: int, dim: int, rot: int, rank: int, head_size: int, write_cache: bool = True,
-                   pairing: str = "interleaved") -> None:
+                   pairing: str = "interleaved", first_head: int = 0) -> None:
     """What latent attention does between its first product and attention (csrc/latent.cu): from qd float32
     [T, heads * (dim + rot) ... | rank + rot at down_offset] the cache row [normed latent | rotated shared key part |
     zeros] into ``pool`` [blocks, 1, 64, head_size], and every head's rotated query part (and zeros behind it) into
-    columns rank .. head_size of its ``q_rows`` [T, heads * head_size] row."""
+    columns rank .. head_size of its ``q_rows`` [T, heads * head_size] row.  ``first_head``: the ``n_heads`` heads of
+    ``q_rows`` are the heads first_head .. first_head + n_heads - 1 of qd (a part of the heads at a time)."""
     n = qd.shape[0]
-    if q_rows.shape != (n, n_heads * head_size) or qd.shape[1] < max(n_heads * (dim + rot), down_offset + rank + rot):
+    shift = int(first_head) * (dim + rot)
+    if (q_rows.shape != (n, n_heads * head_size) or first_head < 0
+            or qd.shape[1] < max(shift + n_heads * (dim + rot), down_offset + rank + rot)):
         raise KernelError("latent_prepare: shapes do not fit")
     if write_cache and tuple(pool.shape[1:]) != (1, 64, head_size):
         raise KernelError("latent_prepare: the cache pool must be [blocks, 1, 64, head_size]")
@@ -1215,8 +1218,9 @@ def latent_prepare(q_rows, pool, qd, down_offset: int, norm_w, eps: float, cos_s
         raise KernelError("latent_prepare: the norm weight or the rotation table does not fit")
     cache_dtype = pool.dtype if write_cache else q_rows.dtype
     _check(_kernels().xrt_latent_prepare(
-        _ptr(q_rows, "q_rows"), _ptr(pool if write_cache else None, "pool"), _ptr(qd, "qd", torch.float32), qd.shape[1],
-        int(down_offset), _ptr(norm_w, "norm_w"), float(eps), _ptr(cos_sin, "cos_sin", torch.float32),
+        _ptr(q_rows, "q_rows"), _ptr(pool if write_cache else None, "pool"),
+        _ptr(qd, "qd", torch.float32) + shift * qd.element_size(), qd.shape[1],
+        int(down_offset) - shift, _ptr(norm_w, "norm_w"), float(eps), _ptr(cos_sin, "cos_sin", torch.float32),
         _ptr(tok_slot, "tok_slot", torch.int32), _ptr(tok_pos, "tok_pos", torch.int32),
         _ptr(block_table, "block_table", torch.int32), block_table.shape[1], n, n_heads, int(dim), int(rot), int(rank),
         int(head_size), 1 if write_cache else 0, 1 if pairing == "interleaved" else 0, _code(norm_w.dtype),

@@ -102,7 +102,7 @@ def scored_decode_split(n_tokens: int, n_kv_heads: int, context: int, window: in
 
 def run(out, q, ctx, store, n_heads, n_kv_heads, head_dim, scale, window, keep_first=0, softcap=0.0,
         distance_rate=0.0, sink=None) -> bool:
-    if n_heads // n_kv_heads > 16:
+    if n_heads // n_kv_heads > 16 or head_dim > 256:
         return False
     # the layer's score options: kernels that take them only
     scored = bool(keep_first or softcap or distance_rate) or sink is not None

@@ -53,9 +53,9 @@ class LatentAttention:
         self.window = params.get("window")
         self.scale = float(params["scale"])
         self.head_size = -(-(self.rank + self.rot) // 16) * 16  # what the attention kernels and the cache see
-        if self.head_size > 256:
+        if self.head_size > 1024:  # rows wider than 256 run on the kernel that takes any case, in both dtypes
             raise Unsupported(f"latent attention: kv_rank + rot_dim = {self.rank + self.rot} exceeds the attention "
-                              f"kernels' head size of 256")
+                              f"kernels' widest row of 1024")
         if self.rot % 2:
             raise ConfigError(f"rot_dim {self.rot} must be even")
         self.w_q_down = weights.get("q_down")
@@ -79,28 +79,36 @@ class LatentAttention:
     def cache_need(self):
         return KVNeed(1, self.head_size, self.window, 0, values_in_keys=True)
 
+    HEADS_A_PASS = 16  # the attention kernels serve up to 16 query heads a kv head: more heads go in several passes
+
     def attended(self, h, ctx, store, owns_cache=True):
         """The heads' values side by side in the compute dtype, [T, heads * v_head_dim]."""
         n = h.shape[0]
         qd = linear(h, self.w_q_down if owns_cache else self.w_q, out_dtype=torch.float32)
-        q = torch.empty((n, self.n_heads * self.head_size), dtype=self.act_dtype, device=h.device)
-        ops.latent_prepare(q, store.k, qd, self.q_rows, self.down_norm, self.eps, self.position.tables(ctx), ctx.tok_slot,
-                           ctx.tok_pos, store.block_table, self.n_heads, self.dim, self.rot, self.rank, self.head_size,
-                           write_cache=owns_cache, pairing=getattr(self.position, "pairing", "interleaved"))
-        # [W_uk^T q_plain] into the first `rank` columns of every head's query row
-        ops.head_product(q, self.head_size, 0, qd, self.dim + self.rot, 0, self.w_uk_t, self.n_heads)
-        padded = sum(ctx.new_lens) < ctx.n_tokens
-        latent = (torch.zeros if padded else torch.empty)(q.shape, dtype=self.act_dtype, device=h.device)
-        window = int(self.window) if self.window else 0
-        done = False
-        if self.dtype is DType.BF16:
-            from . import attention_bf16
-            done = attention_bf16.run(latent, q, ctx, store, self.n_heads, 1, self.head_size, self.scale, window)
-        if not done:
-            ops.attention_reference(latent, q, store.k, store.v, ctx.tok_slot, ctx.tok_pos, store.block_table, self.n_heads,
-                                    1, self.head_size, self.scale, window)
         out = torch.empty((n, self.n_heads * self.vdim), dtype=self.act_dtype, device=h.device)
-        ops.head_product(out, self.vdim, 0, latent, self.head_size, 0, self.w_uv, self.n_heads)
+        padded = sum(ctx.new_lens) < ctx.n_tokens
+        window = int(self.window) if self.window else 0
+        tables = self.position.tables(ctx)
+        pairing = getattr(self.position, "pairing", "interleaved")
+        for first in range(0, self.n_heads, self.HEADS_A_PASS):
+            heads = min(self.HEADS_A_PASS, self.n_heads - first)
+            q = torch.empty((n, heads * self.head_size), dtype=self.act_dtype, device=h.device)
+            ops.latent_prepare(q, store.k, qd, self.q_rows, self.down_norm, self.eps, tables, ctx.tok_slot, ctx.tok_pos,
+                               store.block_table, heads, self.dim, self.rot, self.rank, self.head_size,
+                               write_cache=owns_cache and first == 0, pairing=pairing, first_head=first)
+            # [W_uk^T q_plain] into the first `rank` columns of every head's query row
+            ops.head_product(q, self.head_size, 0, qd, self.dim + self.rot, first * (self.dim + self.rot),
+                             self.w_uk_t[first:first + heads], heads)
+            latent = (torch.zeros if padded else torch.empty)(q.shape, dtype=self.act_dtype, device=h.device)
+            done = False
+            if self.dtype is DType.BF16:
+                from . import attention_bf16
+                done = attention_bf16.run(latent, q, ctx, store, heads, 1, self.head_size, self.scale, window)
+            if not done:
+                ops.attention_reference(latent, q, store.k, store.v, ctx.tok_slot, ctx.tok_pos, store.block_table, heads,
+                                        1, self.head_size, self.scale, window)
+            ops.head_product(out, self.vdim, first * self.vdim, latent, self.head_size, 0, self.w_uv[first:first + heads],
+                             heads)
         return out
 
     def mix(self, h, ctx, store, owns_cache=True):
