@@ -343,6 +343,30 @@ def test_one_small_product_a_head_inside_wider_rows(n, heads, rows, k):
     _close(out.float().cpu().numpy().reshape(n, heads, out_head)[:, :, out_off:out_off + rows], want, 1e-2)
 
 
+@pytest.mark.parametrize("x_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n,heads,rows,k,pad,x_off", [(8, 3, 192, 128, 8, 4), (16, 2, 40, 264, 0, 0), (17, 2, 72, 48, 4, 0),
+                                                      (200, 5, 100, 320, 12, 8), (3, 2, 9, 24, 3, 1), (70, 1, 64, 16, 0, 0)])
+def test_the_product_a_head_on_the_tensor_cores(x_dtype, n, heads, rows, k, pad, x_off):
+    """bfloat16 matrices and results: few rows and many, pieces on 16-byte boundaries (whole vectors) and off them, k
+    beyond one stretch of shared memory, outputs that end inside a tile; rows of a step alone give the same bits."""
+    from xeno_rt_b200.csrc import ops
+    rng = np.random.default_rng(15)
+    x_head, out_head, out_off = k + pad, rows + 2, 1
+    x, w = _bf16(rng.normal(size=(n, heads * x_head))), _bf16(rng.normal(size=(heads, rows, k)))
+    xt = _t(x) if x_dtype == "float32" else _t(x).to(torch.bfloat16)
+    wt = _t(w).to(torch.bfloat16)
+    want = np.einsum("thk,hnk->thn", x.reshape(n, heads, x_head)[:, :, x_off:x_off + k], w)
+    out = torch.full((n, heads * out_head), 5.0, dtype=torch.bfloat16, device=DEV)
+    ops.head_product(out, out_head, out_off, xt, x_head, x_off, wt, heads)
+    got = out.float().cpu().numpy().reshape(n, heads, out_head)
+    _close(got[:, :, out_off:out_off + rows], want, 6e-3)
+    assert (got[:, :, :out_off] == 5.0).all() and (got[:, :, out_off + rows:] == 5.0).all()
+    alone = torch.zeros((1, heads * out_head), dtype=torch.bfloat16, device=DEV)
+    ops.head_product(alone, out_head, out_off, xt[n - 1:].contiguous(), x_head, x_off, wt, heads)
+    piece = lambda row: row.reshape(heads, out_head)[:, out_off:out_off + rows]
+    assert torch.equal(piece(alone[0]), piece(out[n - 1]))
+
+
 # ------------------------------------------------------------------------------------------------ shared keys
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("own_window,reader_window,reader_heads", [(70, 20, 3), (40, 130, 6), (64, 64, 3)])

@@ -14,7 +14,7 @@
 //                        and the rotated query parts at their place in the attention kernel's query rows
 //   xrt_head_product     out[t, head, n] = sum_k x[t, head, k] W[head, n, k]: one small matrix a head, for both
 //                        W_uk^T (before attention) and W_uv (after it); operands at any offset inside wider rows
-#include "common.cuh"
+#include "attention_mma.cuh"
 
 namespace xrt {
 
@@ -131,6 +131,122 @@ head_product_kernel(TO* __restrict__ out, int out_stride, int out_head, int out_
   }
 }
 
+// The same product on the tensor cores for bfloat16 matrices and results (x 32-bit, rounded first, or bfloat16):
+// m16n8k16 steps over k in rising order with 32-bit sums, so a token's result does not depend on the tile it is in.
+// 4 warps.  WM = 4: a block is 64 tokens x 64 outputs, a warp 16 tokens x 64; WM = 1 (a step of few tokens): 16 tokens
+// x 32 outputs, a warp 8 outputs, and all of k (up to BK) is in flight at once.  VEC: every piece starts on a 16-byte
+// (x: 4 elements) boundary and k is a multiple of 8; otherwise element by element.
+template <typename TX, int WM, int NT, int BK, bool VEC>
+__global__ void __launch_bounds__(128)
+head_product_mma_kernel(__nv_bfloat16* __restrict__ out, int out_stride, int out_head, int out_off,
+                        const TX* __restrict__ x, int x_stride, int x_head, int x_off,
+                        const __nv_bfloat16* __restrict__ w, int n_tokens, int n, int k) {
+  constexpr int BM = 16 * WM, BN = (4 / WM) * NT * 8, LD = BK + 8;
+  __shared__ __align__(16) __nv_bfloat16 xs[BM][LD];
+  __shared__ __align__(16) __nv_bfloat16 ws[BN][LD];
+  pdl_trigger();
+  pdl_wait();
+  const int t0 = blockIdx.x * BM, head = blockIdx.y, n0 = blockIdx.z * BN;
+  const TX* xh = x + (size_t)head * x_head + x_off;
+  const __nv_bfloat16* wh = w + (size_t)head * n * k;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+  const int row0 = (warp % WM) * 16, col0 = (warp / WM) * NT * 8;
+  float acc[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+  for (int k0 = 0; k0 < k; k0 += BK) {
+    if (VEC) {
+#pragma unroll 4
+      for (int e = threadIdx.x; e < BM * (BK / 4); e += 128) {
+        const int r = e / (BK / 4), c = (e - r * (BK / 4)) * 4;
+        uint2 v = make_uint2(0u, 0u);
+        if (t0 + r < n_tokens && k0 + c < k) {
+          const TX* src = xh + (size_t)(t0 + r) * x_stride + k0 + c;
+          if constexpr (sizeof(TX) == 4) {
+            const float4 f = *reinterpret_cast<const float4*>(src);
+            v = make_uint2(pack_bf16(f.x, f.y), pack_bf16(f.z, f.w));
+          } else {
+            v = *reinterpret_cast<const uint2*>(src);
+          }
+        }
+        *reinterpret_cast<uint2*>(&xs[r][c]) = v;
+      }
+#pragma unroll 4
+      for (int e = threadIdx.x; e < BN * (BK / 8); e += 128) {
+        const int r = e / (BK / 8), c = (e - r * (BK / 8)) * 8;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (n0 + r < n && k0 + c < k) v = *reinterpret_cast<const uint4*>(wh + (size_t)(n0 + r) * k + k0 + c);
+        *reinterpret_cast<uint4*>(&ws[r][c]) = v;
+      }
+    } else {
+      for (int e = threadIdx.x; e < BM * BK; e += 128) {
+        const int r = e / BK, c = e - r * BK;
+        float v = 0.f;
+        if (t0 + r < n_tokens && k0 + c < k) v = to_float(xh[(size_t)(t0 + r) * x_stride + k0 + c]);
+        xs[r][c] = __float2bfloat16_rn(v);
+      }
+      for (int e = threadIdx.x; e < BN * BK; e += 128) {
+        const int r = e / BK, c = e - r * BK;
+        ws[r][c] = (n0 + r < n && k0 + c < k) ? wh[(size_t)(n0 + r) * k + k0 + c] : __float2bfloat16_rn(0.f);
+      }
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int kk = 0; kk < BK; kk += 16) {
+      if (k0 + kk >= k) break;
+      uint32_t a[4];
+      a[0] = *reinterpret_cast<const uint32_t*>(&xs[row0 + g][kk + 2 * tq]);
+      a[1] = *reinterpret_cast<const uint32_t*>(&xs[row0 + g + 8][kk + 2 * tq]);
+      a[2] = *reinterpret_cast<const uint32_t*>(&xs[row0 + g][kk + 8 + 2 * tq]);
+      a[3] = *reinterpret_cast<const uint32_t*>(&xs[row0 + g + 8][kk + 8 + 2 * tq]);
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        const __nv_bfloat16* wr = &ws[col0 + j * 8 + g][kk + 2 * tq];
+        mma_16816(acc[j], a, *reinterpret_cast<const uint32_t*>(wr), *reinterpret_cast<const uint32_t*>(wr + 8));
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int j = 0; j < NT; ++j)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int t = t0 + row0 + g + (i >> 1) * 8, c = n0 + col0 + j * 8 + 2 * tq + (i & 1);
+      if (t < n_tokens && c < n)
+        out[(size_t)t * out_stride + (size_t)head * out_head + out_off + c] = __float2bfloat16_rn(acc[j][i]);
+    }
+}
+
+template <typename TX, int WM, int NT, int BK>
+static void launch_head_product_mma(bool vec, void* out, int out_stride, int out_head, int out_off, const void* x,
+                                    int x_stride, int x_head, int x_off, const void* w, int n_tokens, int n_heads, int n,
+                                    int k, cudaStream_t stream) {
+  constexpr int BM = 16 * WM, BN = (4 / WM) * NT * 8;
+  const dim3 grid((n_tokens + BM - 1) / BM, n_heads, (n + BN - 1) / BN);
+  if (vec)
+    launch_kernel(head_product_mma_kernel<TX, WM, NT, BK, true>, grid, dim3(128), 0, stream, (__nv_bfloat16*)out,
+                  out_stride, out_head, out_off, (const TX*)x, x_stride, x_head, x_off, (const __nv_bfloat16*)w, n_tokens, n, k);
+  else
+    launch_kernel(head_product_mma_kernel<TX, WM, NT, BK, false>, grid, dim3(128), 0, stream, (__nv_bfloat16*)out,
+                  out_stride, out_head, out_off, (const TX*)x, x_stride, x_head, x_off, (const __nv_bfloat16*)w, n_tokens, n, k);
+}
+
+template <typename TX>
+static void head_product_mma(void* out, int out_stride, int out_head, int out_off, const void* x, int x_stride,
+                             int x_head, int x_off, const void* w, int n_tokens, int n_heads, int n, int k,
+                             cudaStream_t stream) {
+  const bool vec = k % 8 == 0 && x_stride % 4 == 0 && x_head % 4 == 0 && x_off % 4 == 0 &&
+                   (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0;
+  if (n_tokens <= 16)
+    launch_head_product_mma<TX, 1, 1, 256>(vec, out, out_stride, out_head, out_off, x, x_stride, x_head, x_off, w,
+                                           n_tokens, n_heads, n, k, stream);
+  else
+    launch_head_product_mma<TX, 4, 8, 32>(vec, out, out_stride, out_head, out_off, x, x_stride, x_head, x_off, w,
+                                          n_tokens, n_heads, n, k, stream);
+}
+
 }  // namespace xrt
 
 // q_rows [T, heads * head_size] in q_dtype; pool [blocks, 1, 64, head_size] in cache_dtype (null with write_cache 0);
@@ -163,6 +279,15 @@ XRT_EXPORT int xrt_head_product(void* out, int out_stride, int out_head, int out
   if (n_tokens < 0 || n_heads <= 0 || n <= 0 || k <= 0) return XRT_ERR_ARGUMENT;
   if (n_heads > 65535 || (n + xrt::HP_N - 1) / xrt::HP_N > 65535) return XRT_ERR_UNSUPPORTED;
   if (n_tokens == 0) return XRT_OK;
+  if (w_dtype == XRT_BF16 && out_dtype == XRT_BF16 && (x_dtype == XRT_F32 || x_dtype == XRT_BF16)) {
+    if (x_dtype == XRT_F32)
+      xrt::head_product_mma<float>(out, out_stride, out_head, out_off, x, x_stride, x_head, x_off, w, n_tokens, n_heads,
+                                   n, k, stream);
+    else
+      xrt::head_product_mma<__nv_bfloat16>(out, out_stride, out_head, out_off, x, x_stride, x_head, x_off, w, n_tokens,
+                                           n_heads, n, k, stream);
+    return xrt::launch_status();
+  }
   const dim3 grid((n_tokens + xrt::HP_T - 1) / xrt::HP_T, n_heads, (n + xrt::HP_N - 1) / xrt::HP_N);
   XRT_DISPATCH_DTYPE(x_dtype, TX, {
     XRT_DISPATCH_DTYPE(w_dtype, TW, {

@@ -9,6 +9,7 @@ from .context import context_bucket
 DECODE_BLOCKS_PER_SM = 3   # 70 KB of shared memory a block at head size 128
 TCGEN05_MIN_NEW = 32       # prompts at least this long use the tcgen05 attention (tiles of 128 query rows)
 FUSED_COMBINE_MAX = 32     # (tokens x kv heads) up to which the splits are merged inside the attention kernel (measured again with 6 splits at 8 sequences: the second kernel is still faster there)
+FUSED_COMBINE_WIDTH = 1024 # (query heads a kv head x head size) up to which the last block merges: one block walks splits x this many numbers
 SPLIT_OVERHEAD_TILES = 2   # what a block costs beside its tiles (query load, merge, partials), in tiles of 64 keys
 CLUSTER_MAX_SPLITS = 16   # up to ops.Tuning.decode_cluster_pairs (token, kv head) pairs the kernel runs a pair's splits
 #                            as one thread-block cluster that merges itself through distributed shared memory (csrc/
@@ -124,7 +125,9 @@ def run(out, q, ctx, store, n_heads, n_kv_heads, head_dim, scale, window, keep_f
         chunk, n_splits, clusters = _decode_split_of(ctx, n_kv_heads, q.device, window)
         # few sequences: the last block of a (token, kv head) merges its splits (one launch less);
         # many: a second kernel merges them with more threads (measured faster from 8 sequences on)
-        fused = ctx.n_tokens * n_kv_heads <= FUSED_COMBINE_MAX
+        # (a group's partial results of more than FUSED_COMBINE_WIDTH numbers a split are too much for one block)
+        fused = (ctx.n_tokens * n_kv_heads <= FUSED_COMBINE_MAX
+                 and (n_heads // n_kv_heads) * head_dim <= FUSED_COMBINE_WIDTH)
         ops.attention_decode(out, q, store.k, store.v, ctx.tok_slot, ctx.tok_pos, store.block_table, n_heads,
                              n_kv_heads, head_dim, scale, window, chunk, n_splits, fused=fused, clusters=clusters)
         return True
