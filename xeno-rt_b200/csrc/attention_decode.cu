@@ -969,7 +969,8 @@ static int attention_decode_impl(void* out, float* part_o, float* part_ml, const
   if (merged_out != nullptr) *merged_out = merged ? 1 : 0;
   if (n_splits > 1 && counters == nullptr && !merged) {
     const int warps = n_tokens * n_heads;
-    launch_kernel(attention_combine_kernel, dim3((warps * 32 + 255) / 256), dim3(256), 0, stream, o,
+    const int threads = warps <= 1024 ? 64 : 256;  // few rows: two warps a block, so that they spread over the multiprocessors
+    launch_kernel(attention_combine_kernel, dim3((warps * 32 + threads - 1) / threads), dim3(threads), 0, stream, o,
                   (const float*)part_o, (const float*)part_ml, tok_slot, tok_pos, n_tokens, n_heads, head_dim, window,
                   chunk, n_splits);
     return launch_status();

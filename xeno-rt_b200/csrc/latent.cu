@@ -156,29 +156,45 @@ head_product_mma_kernel(__nv_bfloat16* __restrict__ out, int out_stride, int out
   for (int j = 0; j < NT; ++j)
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+  // VEC: a thread's pieces of the next stretch of k wait in registers while the tensor cores work on this one
+  constexpr int XV = BM * (BK / 4) / 128, WV = BN * (BK / 8) / 128;
+  static_assert(BM * (BK / 4) % 128 == 0 && BN * (BK / 8) % 128 == 0, "whole rounds of the block's threads");
+  uint2 xr[XV];
+  uint4 wr4[WV];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int i = 0; i < XV; ++i) {
+      const int e = threadIdx.x + i * 128, r = e / (BK / 4), c = (e - r * (BK / 4)) * 4;
+      xr[i] = make_uint2(0u, 0u);
+      if (t0 + r < n_tokens && k0 + c < k) {
+        const TX* src = xh + (size_t)(t0 + r) * x_stride + k0 + c;
+        if constexpr (sizeof(TX) == 4) {
+          const float4 f = *reinterpret_cast<const float4*>(src);
+          xr[i] = make_uint2(pack_bf16(f.x, f.y), pack_bf16(f.z, f.w));
+        } else {
+          xr[i] = *reinterpret_cast<const uint2*>(src);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < WV; ++i) {
+      const int e = threadIdx.x + i * 128, r = e / (BK / 8), c = (e - r * (BK / 8)) * 8;
+      wr4[i] = make_uint4(0u, 0u, 0u, 0u);
+      if (n0 + r < n && k0 + c < k) wr4[i] = *reinterpret_cast<const uint4*>(wh + (size_t)(n0 + r) * k + k0 + c);
+    }
+  };
+  if (VEC) fetch(0);
   for (int k0 = 0; k0 < k; k0 += BK) {
     if (VEC) {
-#pragma unroll 4
-      for (int e = threadIdx.x; e < BM * (BK / 4); e += 128) {
-        const int r = e / (BK / 4), c = (e - r * (BK / 4)) * 4;
-        uint2 v = make_uint2(0u, 0u);
-        if (t0 + r < n_tokens && k0 + c < k) {
-          const TX* src = xh + (size_t)(t0 + r) * x_stride + k0 + c;
-          if constexpr (sizeof(TX) == 4) {
-            const float4 f = *reinterpret_cast<const float4*>(src);
-            v = make_uint2(pack_bf16(f.x, f.y), pack_bf16(f.z, f.w));
-          } else {
-            v = *reinterpret_cast<const uint2*>(src);
-          }
-        }
-        *reinterpret_cast<uint2*>(&xs[r][c]) = v;
+#pragma unroll
+      for (int i = 0; i < XV; ++i) {
+        const int e = threadIdx.x + i * 128, r = e / (BK / 4), c = (e - r * (BK / 4)) * 4;
+        *reinterpret_cast<uint2*>(&xs[r][c]) = xr[i];
       }
-#pragma unroll 4
-      for (int e = threadIdx.x; e < BN * (BK / 8); e += 128) {
-        const int r = e / (BK / 8), c = (e - r * (BK / 8)) * 8;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (n0 + r < n && k0 + c < k) v = *reinterpret_cast<const uint4*>(wh + (size_t)(n0 + r) * k + k0 + c);
-        *reinterpret_cast<uint4*>(&ws[r][c]) = v;
+#pragma unroll
+      for (int i = 0; i < WV; ++i) {
+        const int e = threadIdx.x + i * 128, r = e / (BK / 8), c = (e - r * (BK / 8)) * 8;
+        *reinterpret_cast<uint4*>(&ws[r][c]) = wr4[i];
       }
     } else {
       for (int e = threadIdx.x; e < BM * BK; e += 128) {
@@ -193,6 +209,7 @@ head_product_mma_kernel(__nv_bfloat16* __restrict__ out, int out_stride, int out
       }
     }
     __syncthreads();
+    if (VEC && k0 + BK < k) fetch(k0 + BK);
 #pragma unroll 4
     for (int kk = 0; kk < BK; kk += 16) {
       if (k0 + kk >= k) break;
