@@ -197,15 +197,14 @@ def test_blended_rotation_table(scaling):
     dims, base = 24, 5000.0
     part = part_class("position", "blended_rotary")({"rope_dim": dims, "base": base, "scaling": scaling}, {}, None, DEV)
     assert part.pairing == "interleaved"
-    positions = [0, 1, 63, 64, 65, 700, 5000]
+    positions = [0, 1, 63, 64, 65, 700, 5000, 300001, 8000003]
     ctx = SimpleNamespace(shared={}, n_tokens=len(positions), tok_pos=ints(positions))
     table = part.tables(ctx).cpu().numpy()
     f, mult = plain.yarn_frequencies(dims, base, scaling)
     angle = np.array(positions)[:, None] * f[None, :]
     want = np.stack([np.cos(angle), np.sin(angle)], axis=-1) * mult
-    # 32-bit angles: an angle of 5,000 radians is known to 2.5e-4
-    assert np.abs(table - want).max() < 1e-3
-    assert np.abs(table[:5] - want[:5]).max() < 2e-5
+    # the 32-bit product's rounding error is carried along: an angle of millions of radians is as exact as a small one
+    assert np.abs(table - want).max() < 3e-6
     if scaling and scaling["factor"] == 4.0:  # the blend matters: neither the plain nor the fully divided frequencies
         plain_f, _ = plain.yarn_frequencies(dims, base, None)
         assert np.abs(f - plain_f).max() > 1e-3 and np.abs(f - plain_f / 4.0).max() > 1e-3

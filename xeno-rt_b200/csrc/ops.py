@@ -30,7 +30,7 @@ _SIGNATURES = {
     "xrt_rmsnorm": [_P, _P, _P, _P, _I, _I, _F, _I, _I, _P],
     "xrt_layernorm": [_P, _P, _P, _P, _I, _I, _F, _I, _I, _P],
     "xrt_swiglu": [_P, _P, _I, _I, _I, _I, _P],
-    "xrt_rotation_table": [_P, _P, _P, _F, _I, _I, _P],
+    "xrt_rotation_table": [_P, _P, _P, _P, _F, _I, _I, _P],
     "xrt_state_scan": [_P, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "xrt_short_conv": [_P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "xrt_ssd_scan": [_P, _P, _I, _P, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
@@ -783,13 +783,18 @@ def _columns(t, name: str, width: int):
     return t.data_ptr(), t.stride(0)
 
 
-def rotation_table(cos_sin, positions, freq, magnitude: float = 1.0) -> None:
-    """cos_sin[t, i] = magnitude * (cos, sin)(positions[t] * freq[i]); cos_sin is float32 [T, half, 2]."""
+def rotation_table(cos_sin, positions, freq, magnitude: float = 1.0, freq_lo=None) -> None:
+    """cos_sin[t, i] = magnitude * (cos, sin)(positions[t] * freq[i]); cos_sin is float32 [T, half, 2].  ``freq_lo``
+    (float32 [half]): what ``freq`` lost of its 64-bit value; with it the product's rounding error is carried too, so
+    that the angle of a far position is as exact as that of a near one."""
     n, half = cos_sin.shape[0], cos_sin.shape[1]
     if positions.numel() != n or freq.numel() != half or cos_sin.shape[2] != 2:
         raise KernelError("rotation_table: shapes do not fit")
+    if freq_lo is not None and freq_lo.numel() != half:
+        raise KernelError("rotation_table: freq_lo must have one entry a frequency")
     _check(_kernels().xrt_rotation_table(_ptr(cos_sin, "cos_sin", torch.float32),
                                         _ptr(positions, "positions", torch.int32), _ptr(freq, "freq", torch.float32),
+                                        None if freq_lo is None else _ptr(freq_lo, "freq_lo", torch.float32),
                                         float(magnitude), n, half, _stream()), "rotation_table")
 
 

@@ -29,17 +29,30 @@ __global__ void rope_table_kernel(float2* __restrict__ cos_sin, const int* __res
 }
 
 // cos_sin[t, i] = magnitude * (cos, sin) of pos[t] * freq[i]: a table of frequencies of any make (scaled,
-// blended between two scalings) and one factor on both cos and sin.  The angle is one 32-bit product.
+// blended between two scalings) and one factor on both cos and sin.  The angle is one 32-bit product; with freq_lo
+// (what the 32-bit frequency lost of its 64-bit value) the product's own rounding error and pos * freq_lo are kept as
+// a second 32-bit term d, and cos(a + d) = cos a cos d - sin a sin d, sin(a + d) = sin a cos d + cos a sin d: a far
+// position's angle is then as exact as a near one's.
 __global__ void rotation_table_kernel(float2* __restrict__ cos_sin, const int* __restrict__ pos,
-                                      const float* __restrict__ freq, float magnitude, int n_tokens, int half) {
+                                      const float* __restrict__ freq, const float* __restrict__ freq_lo, float magnitude,
+                                      int n_tokens, int half) {
   pdl_trigger();
   pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_tokens * half) return;
   const int t = i / half, p = i - t * half;
-  const float angle = __fmul_rn((float)pos[t], freq[p]);
+  const float position = (float)pos[t];
+  const float angle = __fmul_rn(position, freq[p]);
   float s, c;
   sincosf(angle, &s, &c);
+  if (freq_lo != nullptr) {
+    const float d = __fmaf_rn(position, freq_lo[p], __fmaf_rn(position, freq[p], -angle));
+    float sd, cd;
+    sincosf(d, &sd, &cd);
+    const float c0 = c;
+    c = __fmaf_rn(c0, cd, -s * sd);
+    s = __fmaf_rn(s, cd, c0 * sd);
+  }
   cos_sin[i] = make_float2(c * magnitude, s * magnitude);
 }
 
@@ -324,13 +337,14 @@ XRT_EXPORT int xrt_rope_table(float* cos_sin, const int* pos, const float* freq,
   return xrt::launch_status();
 }
 
-XRT_EXPORT int xrt_rotation_table(float* cos_sin, const int* pos, const float* freq, float magnitude, int n_tokens,
-                                  int half, cudaStream_t stream) {
+// freq_lo may be null (the angle is then the 32-bit product alone).
+XRT_EXPORT int xrt_rotation_table(float* cos_sin, const int* pos, const float* freq, const float* freq_lo, float magnitude,
+                                  int n_tokens, int half, cudaStream_t stream) {
   if (n_tokens < 0 || half < 0) return XRT_ERR_ARGUMENT;
   const int total = n_tokens * half;
   if (total == 0) return XRT_OK;
   xrt::launch_kernel(xrt::rotation_table_kernel, dim3((total + 255) / 256), dim3(256), 0, stream, (float2*)cos_sin, pos,
-                     freq, magnitude, n_tokens, half);
+                     freq, freq_lo, magnitude, n_tokens, half);
   return xrt::launch_status();
 }
 

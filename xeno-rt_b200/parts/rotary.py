@@ -61,8 +61,9 @@ class BlendedRotaryEncoding:
     hi = min(ceil(d(slow)), rope_dim - 1); cos and sin are multiplied by 0.1 ln(factor) + 1.
     params: ``rope_dim``, ``base``, ``pairing``, and ``scaling`` = None or a dict with ``factor``,
     ``original`` (positions the frequencies were made for), ``fast`` and ``slow`` (turns over those
-    positions).  No weights.  The frequencies are worked out once in float64 and kept in 32-bit; a
-    step's angles are 32-bit products of position and frequency."""
+    positions).  No weights.  The frequencies are worked out once in float64 and kept as two 32-bit
+    terms; a step's angles are 32-bit products of position and frequency whose rounding error is carried along, so
+    that far positions turn as exactly as near ones."""
 
     @classmethod
     def weight_shapes(cls, params):
@@ -95,6 +96,8 @@ class BlendedRotaryEncoding:
             freq = freq / factor * ramp + freq * (1.0 - ramp)
             self.magnitude = 0.1 * math.log(factor) + 1.0
         self.freq = torch.from_numpy(freq.astype(np.float32)).to(device)
+        # what the 32-bit frequency lost: the table kernel carries it, and its product's rounding error, into the angle
+        self.freq_lo = torch.from_numpy((freq - freq.astype(np.float32).astype(np.float64)).astype(np.float32)).to(device)
         self._key = ("blended_rotary", self.rope_dim, self.base, repr(sorted((scaling or {}).items())))
 
     def tables(self, ctx):
@@ -102,7 +105,7 @@ class BlendedRotaryEncoding:
         table = ctx.shared.get(self._key)
         if table is None:
             table = torch.empty((ctx.n_tokens, self.half, 2), dtype=torch.float32, device=self.freq.device)
-            ops.rotation_table(table, ctx.tok_pos, self.freq, self.magnitude)
+            ops.rotation_table(table, ctx.tok_pos, self.freq, self.magnitude, freq_lo=self.freq_lo)
             ctx.shared[self._key] = table
         return table
 
