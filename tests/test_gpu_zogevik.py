@@ -4,6 +4,7 @@ into portions down to two tokens, batches of unequal requests, slots and blocks 
 over decoded tokens and give their blocks back, long decoding through captured steps, greedy generation through the
 scheduler, and the trace replay program."""
 import copy
+import os
 
 import numpy as np
 import pytest
@@ -235,6 +236,32 @@ def test_greedy_generation_through_the_scheduler(cases, dtype):
             if top[1] - top[0] > 2 * tol * scale:
                 assert int(token) == int(np.argmax(row)), (i, token)
     session.backend.engine.cache.check()
+
+
+def test_the_command_line_generates_what_the_session_generates(cases):
+    """``xrt generate --model DIR`` picks the design by config.json: greedy tokens equal the session's; sampling with
+    a seed repeats itself and differs from another seed."""
+    import subprocess
+    import sys
+    from xeno_rt_b200 import GenerateRequest, Runtime
+    folder, config, _ = cases["odd"]
+    prompts = random_prompts(config["vocab"], [4, 31], seed=8)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    xrt = [sys.executable, os.path.join(root, "bin", "xrt"), "generate", "--model", folder, "--dtype", "float32",
+           "--max-tokens", "9", "--stop-ids", "", "--prompt-ids", ",".join(map(str, prompts[0])),
+           "--prompt-ids", ",".join(map(str, prompts[1]))]
+    greedy = subprocess.run(xrt + ["--temperature", "0", "--repetition-penalty", "1.0"], capture_output=True, text=True,
+                            timeout=600)
+    assert greedy.returncode == 0, greedy.stderr
+    session = Runtime.load(folder, dtype="float32").new_session()
+    results, _ = session.generate_batch([GenerateRequest(p, max_tokens=9, temperature=0.0, repetition_penalty=1.0,
+                                                         stop_ids=()) for p in prompts])
+    lines = [list(map(int, l.split(","))) for l in greedy.stdout.strip().splitlines() if l]
+    assert lines == [list(r.tokens) for r in results]
+    sampled = [subprocess.run(xrt + ["--temperature", "1.3", "--top-k", "20", "--seed", seed], capture_output=True,
+                              text=True, timeout=600) for seed in ("5", "5", "6")]
+    assert all(run.returncode == 0 for run in sampled)
+    assert sampled[0].stdout == sampled[1].stdout != sampled[2].stdout
 
 
 def test_a_model_without_a_file_is_drawn_from_a_seed():

@@ -13,7 +13,9 @@
 //                        of the shared key part and of every head's rotated query part (32-bit angles), the cache row,
 //                        and the rotated query parts at their place in the attention kernel's query rows
 //   xrt_head_product     out[t, head, n] = sum_k x[t, head, k] W[head, n, k]: one small matrix a head, for both
-//                        W_uk^T (before attention) and W_uv (after it); operands at any offset inside wider rows
+//                        W_uk^T (before attention) and W_uv (after it); operands at any offset inside wider rows.
+//                        bfloat16 matrices and results run on the tensor cores (m16n8k16, 32-bit sums), in a form for
+//                        prompts and one for steps of up to 16 tokens; everything else by 32-bit multiply-adds
 #include "attention_mma.cuh"
 
 namespace xrt {
