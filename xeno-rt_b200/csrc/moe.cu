@@ -171,65 +171,104 @@ __global__ void moe_route_kernel(int* __restrict__ ids, float* __restrict__ weig
   for (int c = lane; c < top; c += 32) weights[(size_t)t * top + c] /= sum;
 }
 
-// Dot product of a weight row with a vector in shared memory, 16 bytes of the row a lane and step where VEC
-// (the row's length a multiple of 16 bytes' worth and the row 16-byte aligned), else one element a lane and step.
-template <typename TW, bool VEC>
-__device__ __forceinline__ float row_dot(const TW* __restrict__ row, const float* __restrict__ x, int n, int lane) {
+// R dot products of weight rows with one vector in shared memory at once (rows[i] null: none), 16 bytes of a row a
+// lane and step where VEC (the row's length a multiple of 16 bytes' worth and the rows 16-byte aligned), else one
+// element a lane and step; a row's sum runs over k in rising order a lane, then over the lanes, whatever R is.  A
+// warp has R rows' loads of DEPTH steps in flight and reads the vector once for all of them.
+template <typename TW, bool VEC, int R, int DEPTH>
+__device__ __forceinline__ void rows_dot(float (&out)[R], const TW* const (&rows)[R], const float* __restrict__ x, int n,
+                                         int lane) {
   constexpr int PER = 16 / (int)sizeof(TW);
-  float acc = 0.f;
-  if (VEC) {
-    for (int k = lane * PER; k < n; k += 32 * PER) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(row + k);
-      const TW* v = reinterpret_cast<const TW*>(&raw);
+  float acc[R];
 #pragma unroll
-      for (int j = 0; j < PER; ++j) acc = fmaf(to_float(v[j]), x[k + j], acc);
+  for (int i = 0; i < R; ++i) acc[i] = 0.f;
+  if (VEC) {
+#pragma unroll DEPTH
+    for (int k = lane * PER; k < n; k += 32 * PER) {
+      uint4 raw[R];
+#pragma unroll
+      for (int i = 0; i < R; ++i)
+        raw[i] = rows[i] != nullptr ? *reinterpret_cast<const uint4*>(rows[i] + k) : make_uint4(0u, 0u, 0u, 0u);
+      float xv[PER];
+#pragma unroll
+      for (int j = 0; j < PER; ++j) xv[j] = x[k + j];
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        const TW* v = reinterpret_cast<const TW*>(&raw[i]);
+#pragma unroll
+        for (int j = 0; j < PER; ++j) acc[i] = fmaf(to_float(v[j]), xv[j], acc[i]);
+      }
     }
   } else {
-    for (int k = lane; k < n; k += 32) acc = fmaf(to_float(row[k]), x[k], acc);
+    for (int k = lane; k < n; k += 32) {
+      const float xv = x[k];
+#pragma unroll
+      for (int i = 0; i < R; ++i)
+        if (rows[i] != nullptr) acc[i] = fmaf(to_float(rows[i][k]), xv, acc[i]);
+    }
   }
-  return warp_sum(acc);
+#pragma unroll
+  for (int i = 0; i < R; ++i) out[i] = warp_sum(acc[i]);
 }
 
 // First half of a (token, choice) pair: act[pair][j] for the hidden units j of this block (UNITS a block, one warp a
 // unit at a time).  grid (tokens, top, ceil(ff / UNITS)).
-constexpr int MOE_UNITS = 32;
-template <typename TX, typename TW, bool VEC>
-__global__ void __launch_bounds__(256)
+// UNITS = 32: a warp takes four units (or the gate and up rows of two) at a time; UNITS = 8 (few pairs: more,
+// smaller blocks so that every multiprocessor streams): one unit a warp, its row's loads further ahead instead.
+constexpr int MOE_UNITS = 32, MOE_UNITS_FEW = 8, MOE_WARPS = 8;
+template <typename TX, typename TW, bool VEC, int UNITS>
+__global__ void __launch_bounds__(MOE_WARPS * 32)
 moe_experts_in_kernel(float* __restrict__ act, const TX* __restrict__ h, const TW* __restrict__ w_in,
                       const int* __restrict__ ids, int width, int ff, int top, float limit, float alpha, int act_kind) {
   extern __shared__ float hs[];  // [width]
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x, c = blockIdx.y;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+  constexpr int n_warps = MOE_WARPS, R = UNITS / MOE_WARPS, DEPTH = R >= 4 ? 2 : 8, G = R >= 2 ? R / 2 : 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int e = ids[(size_t)t * top + c];
   for (int k = threadIdx.x; k < width; k += blockDim.x) hs[k] = to_float(h[(size_t)t * width + k]);
   __syncthreads();
-  const int j1 = min(ff, (int)(blockIdx.z + 1) * MOE_UNITS);
+  const int j1 = min(ff, (int)(blockIdx.z + 1) * UNITS);
   if (act_kind == MOE_ACT_GELU) {  // one block of ff rows an expert, no gate
     const TW* only = w_in + (size_t)e * ff * width;
-    for (int j = blockIdx.z * MOE_UNITS + warp; j < j1; j += n_warps) {
-      const float u = row_dot<TW, VEC>(only + (size_t)j * width, hs, width, lane);
-      if (lane == 0) act[((size_t)t * top + c) * ff + j] = gelu_erf(u);
+    for (int j = blockIdx.z * UNITS + warp; j < j1; j += R * n_warps) {  // R of the warp's units at a time
+      const TW* rows[R];
+      float u[R];
+#pragma unroll
+      for (int i = 0; i < R; ++i) rows[i] = j + i * n_warps < j1 ? only + (size_t)(j + i * n_warps) * width : nullptr;
+      rows_dot<TW, VEC, R, DEPTH>(u, rows, hs, width, lane);
+#pragma unroll
+      for (int i = 0; i < R; ++i)
+        if (lane == 0 && rows[i] != nullptr) act[((size_t)t * top + c) * ff + j + i * n_warps] = gelu_erf(u[i]);
     }
     return;
   }
   const TW* gate = w_in + (size_t)e * 2 * ff * width;
   const TW* up = gate + (size_t)ff * width;
-  for (int j = blockIdx.z * MOE_UNITS + warp; j < j1; j += n_warps) {
-    float g = row_dot<TW, VEC>(gate + (size_t)j * width, hs, width, lane);
-    float u = row_dot<TW, VEC>(up + (size_t)j * width, hs, width, lane);
-    if (lane == 0) {
-      g = fminf(g, limit);
-      u = fminf(fmaxf(u, -limit), limit);
-      act[((size_t)t * top + c) * ff + j] = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+  for (int j = blockIdx.z * UNITS + warp; j < j1; j += G * n_warps) {  // gate and up rows of G units at a time
+    const TW* rows[2 * G];
+    float gu[2 * G];
+#pragma unroll
+    for (int i = 0; i < G; ++i) {
+      const bool live = j + i * n_warps < j1;
+      rows[2 * i] = live ? gate + (size_t)(j + i * n_warps) * width : nullptr;
+      rows[2 * i + 1] = live ? up + (size_t)(j + i * n_warps) * width : nullptr;
     }
+    rows_dot<TW, VEC, 2 * G, DEPTH>(gu, rows, hs, width, lane);
+#pragma unroll
+    for (int i = 0; i < G; ++i)
+      if (lane == 0 && rows[2 * i] != nullptr) {
+        const float g = fminf(gu[2 * i], limit);
+        const float u = fminf(fmaxf(gu[2 * i + 1], -limit), limit);
+        act[((size_t)t * top + c) * ff + j + i * n_warps] = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+      }
   }
 }
 
 // Second half: out[c][t][r] = weight * (W_down[e] act)[r] for the rows r of this block.  grid (tokens, top, ceil(width / UNITS)).
-template <typename TW, bool VEC>
-__global__ void __launch_bounds__(256)
+template <typename TW, bool VEC, int UNITS>
+__global__ void __launch_bounds__(MOE_WARPS * 32)
 moe_experts_out_kernel(float* __restrict__ out, const float* __restrict__ act, const TW* __restrict__ w_out,
                        const int* __restrict__ ids, const float* __restrict__ weights, int n_tokens, int width, int ff,
                        int top) {
@@ -237,17 +276,24 @@ moe_experts_out_kernel(float* __restrict__ out, const float* __restrict__ act, c
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x, c = blockIdx.y;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+  constexpr int n_warps = MOE_WARPS, R = UNITS / MOE_WARPS, DEPTH = R >= 4 ? 2 : 8;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int e = ids[(size_t)t * top + c];
   const float weight = weights[(size_t)t * top + c];
   for (int k = threadIdx.x; k < ff; k += blockDim.x) ys[k] = act[((size_t)t * top + c) * ff + k];
   __syncthreads();
   const TW* down = w_out + (size_t)e * width * ff;
   float* dst = out + ((size_t)c * n_tokens + t) * width;
-  const int r1 = min(width, (int)(blockIdx.z + 1) * MOE_UNITS);
-  for (int r = blockIdx.z * MOE_UNITS + warp; r < r1; r += n_warps) {
-    const float acc = row_dot<TW, VEC>(down + (size_t)r * ff, ys, ff, lane);
-    if (lane == 0) dst[r] = weight * acc;
+  const int r1 = min(width, (int)(blockIdx.z + 1) * UNITS);
+  for (int r = blockIdx.z * UNITS + warp; r < r1; r += R * n_warps) {  // R of the warp's rows at a time
+    const TW* rows[R];
+    float acc[R];
+#pragma unroll
+    for (int i = 0; i < R; ++i) rows[i] = r + i * n_warps < r1 ? down + (size_t)(r + i * n_warps) * ff : nullptr;
+    rows_dot<TW, VEC, R, DEPTH>(acc, rows, ys, ff, lane);
+#pragma unroll
+    for (int i = 0; i < R; ++i)
+      if (lane == 0 && rows[i] != nullptr) dst[r + i * n_warps] = weight * acc[i];
   }
 }
 
@@ -414,22 +460,27 @@ XRT_EXPORT int xrt_moe_experts(float* out, float* act, const void* h, const void
   if ((size_t)(width > ff ? width : ff) * sizeof(float) > 48 * 1024) return XRT_ERR_UNSUPPORTED;
   const int per = w_dtype == XRT_BF16 ? 8 : 4;
   const bool vec = width % per == 0 && ff % per == 0 && (((uintptr_t)w_in | (uintptr_t)w_out) & 15) == 0;
-  const dim3 grid_in(n_tokens, top, (ff + xrt::MOE_UNITS - 1) / xrt::MOE_UNITS);
-  const dim3 grid_out(n_tokens, top, (width + xrt::MOE_UNITS - 1) / xrt::MOE_UNITS);
+  // few pairs: blocks of 8 units, so that there are about two blocks a multiprocessor or more
+  const bool few = (long long)n_tokens * top * ((ff + xrt::MOE_UNITS - 1) / xrt::MOE_UNITS) < 2 * 148;
+  const int units = few ? xrt::MOE_UNITS_FEW : xrt::MOE_UNITS;
+  const dim3 grid_in(n_tokens, top, (ff + units - 1) / units);
+  const dim3 grid_out(n_tokens, top, (width + units - 1) / units);
+  const dim3 block(xrt::MOE_WARPS * 32);
+#define XRT_EXPERTS(VEC, UNITS)                                                                                           \
+  do {                                                                                                                    \
+    xrt::launch_kernel(xrt::moe_experts_in_kernel<TX, TW, VEC, UNITS>, grid_in, block, (size_t)width * sizeof(float),     \
+                       stream, act, (const TX*)h, (const TW*)w_in, ids, width, ff, top, limit, alpha, act_kind);          \
+    xrt::launch_kernel(xrt::moe_experts_out_kernel<TW, VEC, UNITS>, grid_out, block, (size_t)ff * sizeof(float), stream,  \
+                       out, (const float*)act, (const TW*)w_out, ids, weights, n_tokens, width, ff, top);                 \
+  } while (0)
   XRT_DISPATCH_DTYPE(h_dtype, TX, {
     XRT_DISPATCH_DTYPE(w_dtype, TW, {
-      if (vec) {
-        xrt::launch_kernel(xrt::moe_experts_in_kernel<TX, TW, true>, grid_in, dim3(256), (size_t)width * sizeof(float), stream,
-                           act, (const TX*)h, (const TW*)w_in, ids, width, ff, top, limit, alpha, act_kind);
-        xrt::launch_kernel(xrt::moe_experts_out_kernel<TW, true>, grid_out, dim3(256), (size_t)ff * sizeof(float), stream, out,
-                           (const float*)act, (const TW*)w_out, ids, weights, n_tokens, width, ff, top);
-      } else {
-        xrt::launch_kernel(xrt::moe_experts_in_kernel<TX, TW, false>, grid_in, dim3(256), (size_t)width * sizeof(float), stream,
-                           act, (const TX*)h, (const TW*)w_in, ids, width, ff, top, limit, alpha, act_kind);
-        xrt::launch_kernel(xrt::moe_experts_out_kernel<TW, false>, grid_out, dim3(256), (size_t)ff * sizeof(float), stream, out,
-                           (const float*)act, (const TW*)w_out, ids, weights, n_tokens, width, ff, top);
-      }
+      if (vec && few) XRT_EXPERTS(true, xrt::MOE_UNITS_FEW);
+      else if (vec) XRT_EXPERTS(true, xrt::MOE_UNITS);
+      else if (few) XRT_EXPERTS(false, xrt::MOE_UNITS_FEW);
+      else XRT_EXPERTS(false, xrt::MOE_UNITS);
     });
   });
+#undef XRT_EXPERTS
   return xrt::launch_status();
 }
