@@ -224,7 +224,7 @@ moe_experts_in_kernel(float* __restrict__ act, const TX* __restrict__ h, const T
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x, c = blockIdx.y;
-  constexpr int n_warps = MOE_WARPS, R = UNITS / MOE_WARPS, DEPTH = R >= 4 ? 2 : 8, G = R >= 2 ? R / 2 : 1;
+  constexpr int n_warps = MOE_WARPS, R = UNITS / MOE_WARPS, DEPTH = R >= 4 ? 4 : 8, G = R >= 2 ? R / 2 : 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int e = ids[(size_t)t * top + c];
   for (int k = threadIdx.x; k < width; k += blockDim.x) hs[k] = to_float(h[(size_t)t * width + k]);
@@ -276,7 +276,7 @@ moe_experts_out_kernel(float* __restrict__ out, const float* __restrict__ act, c
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x, c = blockIdx.y;
-  constexpr int n_warps = MOE_WARPS, R = UNITS / MOE_WARPS, DEPTH = R >= 4 ? 2 : 8;
+  constexpr int n_warps = MOE_WARPS, R = UNITS / MOE_WARPS, DEPTH = R >= 4 ? 4 : 8;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int e = ids[(size_t)t * top + c];
   const float weight = weights[(size_t)t * top + c];
