@@ -9,7 +9,7 @@ namespace xrt {
 template <typename TW>
 __global__ void embedding_kernel(float* __restrict__ out, const TW* __restrict__ table,
                                  const int* __restrict__ ids, int hidden, int vocab,
-                                 int* __restrict__ error_flag) {
+                                 int* __restrict__ error_flag, float scale) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
@@ -18,14 +18,14 @@ __global__ void embedding_kernel(float* __restrict__ out, const TW* __restrict__
   if (!ok && threadIdx.x == 0 && error_flag != nullptr) atomicExch(error_flag, 1);
   const TW* row = table + (size_t)(ok ? id : 0) * hidden;
   float* dst = out + (size_t)t * hidden;
-  for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = ok ? to_float(row[c]) : 0.f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = ok ? to_float(row[c]) * scale : 0.f;
 }
 
 // 16 bytes of the table a thread and step (hidden a multiple of 8 for bfloat16, of 4 for float32)
 template <typename TW>
 __global__ void embedding_vec_kernel(float* __restrict__ out, const TW* __restrict__ table,
                                      const int* __restrict__ ids, int hidden, int vocab,
-                                     int* __restrict__ error_flag) {
+                                     int* __restrict__ error_flag, float scale) {
   constexpr int PER = 16 / (int)sizeof(TW);
   pdl_trigger();
   pdl_wait();
@@ -41,7 +41,7 @@ __global__ void embedding_vec_kernel(float* __restrict__ out, const TW* __restri
     const TW* vals = reinterpret_cast<const TW*>(&raw);
     float f[PER];
 #pragma unroll
-    for (int j = 0; j < PER; ++j) f[j] = ok ? to_float(vals[j]) : 0.f;
+    for (int j = 0; j < PER; ++j) f[j] = ok ? to_float(vals[j]) * scale : 0.f;
 #pragma unroll
     for (int j = 0; j < PER; j += 4) *reinterpret_cast<float4*>(dst + c + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
   }
@@ -109,15 +109,15 @@ XRT_EXPORT int xrt_embedding_pair(float* out, const void* table, const void* pai
 }
 
 XRT_EXPORT int xrt_embedding(float* out, const void* table, const int* ids, int n_tokens, int hidden,
-                             int vocab, int table_dtype, int* error_flag, cudaStream_t stream) {
+                             int vocab, int table_dtype, int* error_flag, float scale, cudaStream_t stream) {
   if (n_tokens < 0 || hidden <= 0 || vocab <= 0) return XRT_ERR_ARGUMENT;
   if (n_tokens == 0) return XRT_OK;
   const bool vec = hidden % 8 == 0 && (((uintptr_t)out | (uintptr_t)table) & 15) == 0;
   XRT_DISPATCH_DTYPE(table_dtype, TW, {
     if (vec)
-      xrt::launch_kernel(xrt::embedding_vec_kernel<TW>, dim3(n_tokens), dim3(128), 0, stream, out, (const TW*)table, ids, hidden, vocab, error_flag);
+      xrt::launch_kernel(xrt::embedding_vec_kernel<TW>, dim3(n_tokens), dim3(128), 0, stream, out, (const TW*)table, ids, hidden, vocab, error_flag, scale);
     else
-      xrt::launch_kernel(xrt::embedding_kernel<TW>, dim3(n_tokens), dim3(256), 0, stream, out, (const TW*)table, ids, hidden, vocab, error_flag);
+      xrt::launch_kernel(xrt::embedding_kernel<TW>, dim3(n_tokens), dim3(256), 0, stream, out, (const TW*)table, ids, hidden, vocab, error_flag, scale);
   });
   return xrt::launch_status();
 }

@@ -18,19 +18,40 @@
 //   routing   scores = softmax of the logits over ALL experts; the experts form `groups` equal groups of neighbours, a
 //             group counts by its largest score and only experts of the `keep` best groups can be chosen; the `top`
 //             largest scores among those win, and a chosen expert's weight is its score as it is (no renormalizing)
+//   options of that routing (RouteOptions): scores = sigmoid of each logit instead of the softmax; a `correction` a
+//             expert that is added to the score for every choice (of groups and of experts) but not for the weight; a
+//             group that counts by the sum of its `group_best` largest choice scores instead of the largest; weights
+//             divided by their sum (+ `sum_eps`) and multiplied by `scale`
 #include "common.cuh"
 
 namespace xrt {
 
-constexpr int MOE_ACT_GATED = 0, MOE_ACT_GELU = 1;
+constexpr int MOE_ACT_GATED = 0, MOE_ACT_GELU = 1, MOE_ACT_SILU = 2;
+
+// A third kind of expert (`act` 2): W_down (silu(W_gate h) * (W_up h)), the gated form without limits and without the
+// one added to the up rows: the gated kernels run it with limit = infinity, alpha = 1 and `up_shift` = 0.
+struct GateForm { float limit, alpha, up_shift; };
+inline GateForm gate_form(int act_kind, float limit, float alpha) {
+  if (act_kind == MOE_ACT_SILU) return {INFINITY, 1.0f, 0.0f};
+  return {limit, alpha, 1.0f};
+}
 
 __device__ __forceinline__ float gelu_erf(float z) { return 0.5f * z * (1.0f + erff(z * 0.70710678118654752f)); }
+
+struct RouteOptions {
+  int sigmoid = 0;                    // scores = 1 / (1 + exp(-z)) each, not the softmax over all
+  const float* correction = nullptr;  // [experts]: choice score = score + correction
+  int group_best = 1;                 // a group counts by the sum of so many of its largest choice scores
+  int normalize = 0;                  // weights / (their sum + sum_eps) ...
+  float sum_eps = 0.f;
+  float scale = 1.f;                  // ... times scale
+};
 
 // One warp a token.  Lane l holds logits l, l + 32, ...; group_best [warps][groups] in shared memory.
 template <int PER_LANE>
 __global__ void moe_route_scores_kernel(int* __restrict__ ids, float* __restrict__ weights,
                                         const float* __restrict__ logits, int n_tokens, int n_experts, int top,
-                                        int groups, int keep) {
+                                        int groups, int keep, const RouteOptions opt) {
   extern __shared__ float group_best[];
   pdl_trigger();
   pdl_wait();
@@ -46,28 +67,61 @@ __global__ void moe_route_scores_kernel(int* __restrict__ ids, float* __restrict
     top_z = fmaxf(top_z, z[i]);
   }
   top_z = warp_max(top_z);
-  float sum = 0.f;
+  float score[PER_LANE];  // what a chosen expert's weight is made of; z becomes what the choice goes by
+  if (opt.sigmoid) {
 #pragma unroll
-  for (int i = 0; i < PER_LANE; ++i) {
-    z[i] = lane + 32 * i < n_experts ? expf(z[i] - top_z) : -INFINITY;  // from here on z holds the scores' numerators
-    if (lane + 32 * i < n_experts) sum += z[i];
+    for (int i = 0; i < PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      score[i] = e < n_experts ? 1.0f / (1.0f + expf(-z[i])) : 0.f;
+      z[i] = e < n_experts ? score[i] : -INFINITY;
+    }
+  } else {
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+      z[i] = lane + 32 * i < n_experts ? expf(z[i] - top_z) : -INFINITY;  // from here on z holds the scores' numerators
+      if (lane + 32 * i < n_experts) sum += z[i];
+    }
+    sum = warp_sum(sum);
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+      if (lane + 32 * i < n_experts) z[i] /= sum;
+      score[i] = z[i];
+    }
   }
-  sum = warp_sum(sum);
+  if (opt.correction != nullptr) {
 #pragma unroll
-  for (int i = 0; i < PER_LANE; ++i)
-    if (lane + 32 * i < n_experts) z[i] /= sum;
+    for (int i = 0; i < PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      if (e < n_experts) z[i] += opt.correction[e];
+    }
+  }
   if (keep < groups) {
     float* best_of = group_best + (size_t)warp * groups;
     const int size = n_experts / groups;
     for (int g = 0; g < groups; ++g) {
-      float b = -INFINITY;
+      // the sum of the group's `group_best` largest choice scores (one: the largest), taken one at a time
+      float worth = 0.f;
+      unsigned taken = 0u;  // bit i: this lane's i-th entry went into the sum already
+      for (int r = 0; r < opt.group_best && r < size; ++r) {
+        float b = -INFINITY;
+        int be = 0x7fffffff;
 #pragma unroll
-      for (int i = 0; i < PER_LANE; ++i) {
-        const int e = lane + 32 * i;
-        if (e < n_experts && e / size == g) b = fmaxf(b, z[i]);
+        for (int i = 0; i < PER_LANE; ++i) {
+          const int e = lane + 32 * i;
+          if (e < n_experts && e / size == g && !(taken >> i & 1u) && (z[i] > b || be == 0x7fffffff)) { b = z[i]; be = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float other = __shfl_xor_sync(0xffffffffu, b, o);
+          const int other_e = __shfl_xor_sync(0xffffffffu, be, o);
+          if (other_e != 0x7fffffff && (be == 0x7fffffff || other > b || (other == b && other_e < be))) { b = other; be = other_e; }
+        }
+        if (be == 0x7fffffff) break;
+        if ((be & 31) == lane) taken |= 1u << (be >> 5);
+        worth = r == 0 ? b : worth + b;
       }
-      b = warp_max(b);
-      if (lane == 0) best_of[g] = b;
+      if (lane == 0) best_of[g] = worth;
     }
     __syncwarp();
     // the keep best groups, one at a time (the lower number wins a tie); a taken group's entry becomes +inf
@@ -108,17 +162,34 @@ __global__ void moe_route_scores_kernel(int* __restrict__ ids, float* __restrict
       const int other_e = __shfl_xor_sync(0xffffffffu, best_e, o);
       if (other > best || (other == best && other_e < best_e)) { best = other; best_e = other_e; }
     }
+    float weight = 0.f;  // the chosen expert's score without the correction
     if (best_e >= n_experts) {  // a row of logits that are no numbers (a padding row's): any expert, no weight
       best_e = c;
-      best = 0.f;
+    } else {
+#pragma unroll
+      for (int i = 0; i < PER_LANE; ++i)
+        if (i == (best_e >> 5)) weight = __shfl_sync(0xffffffffu, score[i], best_e & 31);
     }
 #pragma unroll
     for (int i = 0; i < PER_LANE; ++i)
       if (lane + 32 * i == best_e) z[i] = -INFINITY;  // taken
     if (lane == 0) {
       ids[(size_t)t * top + c] = best_e;
-      weights[(size_t)t * top + c] = best;
+      weights[(size_t)t * top + c] = weight;
     }
+  }
+  if (opt.normalize) {  // lane 0 wrote the weights; it adds them up in the order of the choices
+    __syncwarp();
+    if (lane == 0) {
+      float sum = 0.f;
+      for (int c = 0; c < top; ++c) sum += weights[(size_t)t * top + c];
+      const float f = opt.scale / (sum + opt.sum_eps);
+      for (int c = 0; c < top; ++c) weights[(size_t)t * top + c] *= f;
+    }
+  } else if (opt.scale != 1.f) {
+    __syncwarp();
+    if (lane == 0)
+      for (int c = 0; c < top; ++c) weights[(size_t)t * top + c] *= opt.scale;
   }
 }
 
@@ -219,7 +290,8 @@ constexpr int MOE_UNITS = 32, MOE_UNITS_FEW = 8, MOE_WARPS = 8;
 template <typename TX, typename TW, bool VEC, int UNITS>
 __global__ void __launch_bounds__(MOE_WARPS * 32)
 moe_experts_in_kernel(float* __restrict__ act, const TX* __restrict__ h, const TW* __restrict__ w_in,
-                      const int* __restrict__ ids, int width, int ff, int top, float limit, float alpha, int act_kind) {
+                      const int* __restrict__ ids, int width, int ff, int top, float limit, float alpha, float up_shift,
+                      int act_kind) {
   extern __shared__ float hs[];  // [width]
   pdl_trigger();
   pdl_wait();
@@ -261,7 +333,7 @@ moe_experts_in_kernel(float* __restrict__ act, const TX* __restrict__ h, const T
       if (lane == 0 && rows[2 * i] != nullptr) {
         const float g = fminf(gu[2 * i], limit);
         const float u = fminf(fmaxf(gu[2 * i + 1], -limit), limit);
-        act[((size_t)t * top + c) * ff + j + i * n_warps] = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+        act[((size_t)t * top + c) * ff + j + i * n_warps] = g / (1.0f + expf(-alpha * g)) * (u + up_shift);
       }
   }
 }
@@ -342,7 +414,7 @@ __global__ void moe_gather_kernel(TX* __restrict__ out, const TX* __restrict__ h
 // act[r, j] = g * sigmoid(alpha g) * (u + 1) with g = min(gu[r, j], limit), u = clamp(gu[r, ff + j], -limit, limit)
 template <typename TO>
 __global__ void moe_activation_kernel(TO* __restrict__ act, const float* __restrict__ gate_up, size_t total, int ff,
-                                      float limit, float alpha, int act_kind) {
+                                      float limit, float alpha, float up_shift, int act_kind) {
   pdl_trigger();
   pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
@@ -353,7 +425,7 @@ __global__ void moe_activation_kernel(TO* __restrict__ act, const float* __restr
     const size_t r = i / ff, j = i - r * ff;
     const float g = fminf(gate_up[r * 2 * ff + j], limit);
     const float u = fminf(fmaxf(gate_up[r * 2 * ff + ff + j], -limit), limit);
-    act[i] = from_float<TO>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+    act[i] = from_float<TO>(g / (1.0f + expf(-alpha * g)) * (u + up_shift));
   }
 }
 
@@ -397,9 +469,10 @@ XRT_EXPORT int xrt_moe_activation(void* act, const float* gate_up, int n_rows, i
   if (n_rows == 0) return XRT_OK;
   const size_t total = (size_t)n_rows * ff;
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  const xrt::GateForm form = xrt::gate_form(act_kind, limit, alpha);
   XRT_DISPATCH_DTYPE(out_dtype, TO, {
     xrt::launch_kernel(xrt::moe_activation_kernel<TO>, dim3(blocks), dim3(256), 0, stream, (TO*)act, gate_up, total, ff,
-                       limit, alpha, act_kind);
+                       form.limit, form.alpha, form.up_shift, act_kind);
   });
   return xrt::launch_status();
 }
@@ -430,7 +503,16 @@ XRT_EXPORT int xrt_moe_route(int* ids, float* weights, const float* logits, cons
 
 // The second kind of routing (see the top of the file).  logits [T, experts] float32.
 XRT_EXPORT int xrt_moe_route_scores(int* ids, float* weights, const float* logits, int n_tokens, int n_experts, int top,
-                                    int groups, int keep, cudaStream_t stream) {
+                                    int groups, int keep, int sigmoid, const float* correction, int group_best,
+                                    int normalize, float sum_eps, float scale, cudaStream_t stream) {
+  if (group_best < 1) return XRT_ERR_ARGUMENT;
+  xrt::RouteOptions opt;
+  opt.sigmoid = sigmoid;
+  opt.correction = correction;
+  opt.group_best = group_best;
+  opt.normalize = normalize;
+  opt.sum_eps = sum_eps;
+  opt.scale = scale;
   if (n_tokens < 0 || n_experts <= 0 || top <= 0 || groups <= 0 || keep <= 0 || keep > groups || n_experts % groups)
     return XRT_ERR_ARGUMENT;
   if (top > n_experts / groups * keep) return XRT_ERR_ARGUMENT;
@@ -438,7 +520,7 @@ XRT_EXPORT int xrt_moe_route_scores(int* ids, float* weights, const float* logit
   if (n_tokens == 0) return XRT_OK;
   const dim3 grid((n_tokens + 3) / 4), block(128);
   const size_t smem = (size_t)4 * groups * sizeof(float);
-#define XRT_ROUTE(PER) xrt::launch_kernel(xrt::moe_route_scores_kernel<PER>, grid, block, smem, stream, ids, weights, logits, n_tokens, n_experts, top, groups, keep)
+#define XRT_ROUTE(PER) xrt::launch_kernel(xrt::moe_route_scores_kernel<PER>, grid, block, smem, stream, ids, weights, logits, n_tokens, n_experts, top, groups, keep, opt)
   if (n_experts <= 32) XRT_ROUTE(1);
   else if (n_experts <= 64) XRT_ROUTE(2);
   else if (n_experts <= 128) XRT_ROUTE(4);
@@ -466,10 +548,12 @@ XRT_EXPORT int xrt_moe_experts(float* out, float* act, const void* h, const void
   const dim3 grid_in(n_tokens, top, (ff + units - 1) / units);
   const dim3 grid_out(n_tokens, top, (width + units - 1) / units);
   const dim3 block(xrt::MOE_WARPS * 32);
+  const xrt::GateForm form = xrt::gate_form(act_kind, limit, alpha);
 #define XRT_EXPERTS(VEC, UNITS)                                                                                           \
   do {                                                                                                                    \
     xrt::launch_kernel(xrt::moe_experts_in_kernel<TX, TW, VEC, UNITS>, grid_in, block, (size_t)width * sizeof(float),     \
-                       stream, act, (const TX*)h, (const TW*)w_in, ids, width, ff, top, limit, alpha, act_kind);          \
+                       stream, act, (const TX*)h, (const TW*)w_in, ids, width, ff, top, form.limit, form.alpha,          \
+                       form.up_shift, act_kind);                                                                          \
     xrt::launch_kernel(xrt::moe_experts_out_kernel<TW, VEC, UNITS>, grid_out, block, (size_t)ff * sizeof(float), stream,  \
                        out, (const float*)act, (const TW*)w_out, ids, weights, n_tokens, width, ff, top);                 \
   } while (0)

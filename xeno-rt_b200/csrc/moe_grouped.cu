@@ -23,7 +23,7 @@ struct GroupedArgs {
   const int* offsets;          // [experts + 1]
   void* out;                   // act bfloat16 [rows, ff] (first) or float [rows, N] (second)
   int n_experts, n, k, ff;
-  float limit, alpha;
+  float limit, alpha, up_shift;
 };
 
 // MODE 0: second product; 1: first product of gated experts; 2: first product of experts without a gate.
@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(128) moe_grouped_product_kernel(const GroupedA
           const float gate = fminf(acc[0][nt][2 * half + i], g.limit);
           const float up = fminf(fmaxf(acc[W_TILES - 1][nt][2 * half + i], -g.limit), g.limit);
           ((__nv_bfloat16*)g.out)[(size_t)row * g.ff + col] =
-              __float2bfloat16_rn(gate / (1.0f + expf(-g.alpha * gate)) * (up + 1.0f));
+              __float2bfloat16_rn(gate / (1.0f + expf(-g.alpha * gate)) * (up + g.up_shift));
         } else if (MODE == 2) {
           const float u = acc[0][nt][2 * half + i];
           ((__nv_bfloat16*)g.out)[(size_t)row * g.n + col] =
@@ -136,17 +136,25 @@ __global__ void __launch_bounds__(128) moe_grouped_product_kernel(const GroupedA
 }  // namespace xrt
 
 // first == 2: act [rows, n] bfloat16 = gelu(a . w^T) from w [experts, n, k] (experts without a gate).
+// first == 3: as first == 1 with act = silu(gate) * up.
 // first == 1: act [rows, ff] bfloat16 from a [rows, k] and w [experts, 2 ff, k]; else out [rows, n] float32 from
 // a [rows, k] and w [experts, n, k].  offsets [experts + 1] int32 on the device; `rows` is their last entry's bound
 // (the number of (token, choice) pairs).  k must be a multiple of 8 and the bases 16-byte aligned.
 XRT_EXPORT int xrt_moe_grouped_product(void* out, const void* a, const void* w, const int* offsets, int rows, int n_experts,
                                        int n, int k, int ff, float limit, float alpha, int first, cudaStream_t stream) {
+  float up_shift = 1.0f;
+  if (first == 3) {  // gated silu experts: the gated form without limits and without the one added to the up rows
+    first = 1;
+    limit = INFINITY;
+    alpha = 1.0f;
+    up_shift = 0.0f;
+  }
   if (rows < 0 || n_experts <= 0 || n <= 0 || k <= 0 || (first == 1 && (ff <= 0 || n != 2 * ff))) return XRT_ERR_ARGUMENT;
   if (k % 8 || (((uintptr_t)a | (uintptr_t)w) & 15)) return XRT_ERR_UNSUPPORTED;
   if (rows == 0) return XRT_OK;
   xrt::GroupedArgs g;
   g.a = (const __nv_bfloat16*)a; g.w = (const __nv_bfloat16*)w; g.offsets = offsets; g.out = out;
-  g.n_experts = n_experts; g.n = n; g.k = k; g.ff = ff; g.limit = limit; g.alpha = alpha;
+  g.n_experts = n_experts; g.n = n; g.k = k; g.ff = ff; g.limit = limit; g.alpha = alpha; g.up_shift = up_shift;
   const int row_tiles = (rows + xrt::GG_ROWS - 1) / xrt::GG_ROWS + n_experts;  // every expert may leave one tile partly empty
   const int cols = first == 1 ? ff : n;
   const int col_tiles = (cols + xrt::GG_COLS - 1) / xrt::GG_COLS;

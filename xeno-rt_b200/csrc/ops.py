@@ -26,13 +26,18 @@ _F = ctypes.c_float
 _CODES = {torch.float32: 0, torch.bfloat16: 1}
 
 _SIGNATURES = {
-    "xrt_embedding": [_P, _P, _P, _I, _I, _I, _I, _P, _P],
+    "xrt_embedding": [_P, _P, _P, _I, _I, _I, _I, _P, _F, _P],
     "xrt_rmsnorm": [_P, _P, _P, _P, _I, _I, _F, _I, _I, _P],
     "xrt_layernorm": [_P, _P, _P, _P, _I, _I, _F, _I, _I, _P],
-    "xrt_swiglu": [_P, _P, _I, _I, _I, _I, _P],
+    "xrt_swiglu": [_P, _P, _I, _I, _I, _I, _I, _P],
     "xrt_rotation_table": [_P, _P, _P, _P, _F, _I, _I, _P],
-    "xrt_state_scan": [_P, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
-    "xrt_short_conv": [_P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "xrt_state_scan": [_P, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+    "xrt_removal_gates": [_P, _I, _P, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _F, _F, _P],
+    "xrt_rmsnorm_shift": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _I, _I, _P],
+    "xrt_add_row": [_P, _P, _I, _I, _I, _P],
+    "xrt_act_cast": [_P, _P, _I, _I, _I, _I, _I, _P],
+    "xrt_add_scaled_parts": [_P, _P, _P, ctypes.c_longlong, _I, _P],
+    "xrt_short_conv": [_P, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "xrt_ssd_scan": [_P, _P, _I, _P, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "xrt_gated_group_norm": [_P, _P, _P, _I, _P, _I, _I, _I, _F, _I, _P],
     "xrt_moe_route": [_P, _P, _P, _P, _I, _I, _I, _P],
@@ -46,15 +51,15 @@ _SIGNATURES = {
     "xrt_embedding_pair": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "xrt_layernorm_affine": [_P, _P, _P, _I, ctypes.c_longlong, _P, _P, _P, _I, _I, _F, _I, _P, _P, _P],
     "xrt_qkv_heads_write": [_P, _P, _P, _P, _I, _I, _I, _P, _I, _I, _F, _P, _P, _I, _I, _I, _P, _I, _I,
-                            _P, _I, _P, _I, _F, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
-    "xrt_rmsnorm_add": [_P, _P, ctypes.c_longlong, _I, _P, _P, _I, _I, _F, _I, _I, _P],
+                            _P, _I, _P, _I, _F, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "xrt_rmsnorm_add": [_P, _P, ctypes.c_longlong, _I, _P, _P, _I, _I, _F, _I, _I, _P, _P, _F, _P, _P, _F, _P],
     "xrt_cast_rows": [_P, _P, ctypes.c_longlong, _I, _P],
     "xrt_latent_prepare": [_P, _P, _P, _I, _I, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "xrt_head_product": [_P, _I, _I, _I, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _I, _I, _P],
-    "xrt_moe_route_scores": [_P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "xrt_moe_route_scores": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _I, _I, _F, _F, _P],
     "xrt_decay": [_P, _P, _P, _I, _I, _I, _I, _F, _P],
     "xrt_unit_heads": [_P, _I, _I, _I, _I, _F, _I, _F, _P],
-    "xrt_head_norm_gate": [_P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P],
+    "xrt_head_norm_gate": [_P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "xrt_gate_mul": [_P, _P, _I, _I, _I, _I, _I, _I, _P],
     "xrt_rms_scale_add": [_P, _P, _P, _I, _I, _F, _F, _P],
     "xrt_concat_cast": [_P, _P, _P, _I, _I, _I, _P],
@@ -248,15 +253,15 @@ def _check(status: int, what: str) -> None:
     raise KernelError(f"{what}: CUDA launch error {status}")
 
 
-def embedding(out, table, ids, error_flag) -> None:
-    """out[t, :] = table[ids[t], :] as float32; raises error_flag[0] on an id outside the table."""
+def embedding(out, table, ids, error_flag, scale: float = 1.0) -> None:
+    """out[t, :] = table[ids[t], :] * scale as float32; raises error_flag[0] on an id outside the table."""
     n, hidden = out.shape
     vocab = table.shape[0]
     if table.shape[1] != hidden or ids.numel() != n:
         raise KernelError("embedding: shapes do not fit")
     _check(_kernels().xrt_embedding(_ptr(out, "out", torch.float32), _ptr(table, "table"),
                                    _ptr(ids, "ids", torch.int32), n, hidden, vocab, _code(table.dtype),
-                                   _ptr(error_flag, "error_flag", torch.int32), _stream()), "embedding")
+                                   _ptr(error_flag, "error_flag", torch.int32), float(scale), _stream()), "embedding")
 
 
 def rmsnorm(out, x, weight, eps: float, rows=None) -> None:
@@ -283,13 +288,18 @@ def layernorm(out, x, weight, eps: float, rows=None) -> None:
                                    _code(weight.dtype), _code(out.dtype), _stream()), "layernorm")
 
 
-def swiglu(out, gate_up) -> None:
-    """out[t, f] = silu(gate_up[t, f]) * gate_up[t, F + f]."""
+GATE_ACTS = {"silu": 0, "gelu_tanh": 1}
+
+
+def swiglu(out, gate_up, act: str = "silu") -> None:
+    """out[t, f] = act(gate_up[t, f]) * gate_up[t, F + f]; ``act`` "silu" or "gelu_tanh" (the tanh form of gelu)."""
+    if act not in GATE_ACTS:
+        raise KernelError(f"swiglu: the gate's activation {act!r} is not one of {sorted(GATE_ACTS)}")
     n, width = out.shape
     if gate_up.shape[0] != n or gate_up.shape[1] != 2 * width:
         raise KernelError("swiglu: shapes do not fit")
     _check(_kernels().xrt_swiglu(_ptr(out, "out"), _ptr(gate_up, "gate_up"), n, width, _code(gate_up.dtype),
-                                _code(out.dtype), _stream()), "swiglu")
+                                _code(out.dtype), GATE_ACTS[act], _stream()), "swiglu")
 
 
 def rope_table(cos_sin, positions, freq, scale: float) -> None:
@@ -773,7 +783,7 @@ def mark_seen(seen, slots, ids, vocab: int) -> None:
 
 # ---------------------------------------------------------------------------------------------------
 # Mixers with a matrix state, and the small steps around them (csrc/state_mixers.cu)
-_ACTS = {None: 0, "none": 0, "silu": 1, "sigmoid": 2}
+_ACTS = {None: 0, "none": 0, "silu": 1, "sigmoid": 2, "tanh": 3}
 
 
 def _columns(t, name: str, width: int):
@@ -799,13 +809,18 @@ def rotation_table(cos_sin, positions, freq, magnitude: float = 1.0, freq_lo=Non
 
 
 def state_scan(out, q, k, v, decay, beta, state, cu_seqlens, seq_slot, n_heads: int, n_qk_heads: int, dim: int,
-               vdim: int, q_scale: float = 1.0, delta: bool = False, max_new: int = 0) -> None:
+               vdim: int, q_scale: float = 1.0, delta: bool = False, max_new: int = 0, unit=None, removal=None) -> None:
     """The scan of a matrix state over the step's tokens, a sequence after the other in parallel:
     S <- diag(decay_t) S + k_t u_t^T and out_t = S^T (q_t * q_scale), with u_t = v_t, or with ``delta``
     u_t = sigmoid(beta_t) (v_t - S^T k_t) taken after the decay.  q, k [T, n_qk_heads * dim], v [T, n_heads * vdim],
     decay [T, n_heads * dim] (rows may be slices of wider rows), beta [T, n_heads] before its sigmoid, all
     float32; ``state`` float32 [slots, n_heads, vdim, dim] is read and left as the sequences' last state.
-    ``max_new`` (0: not known): the most tokens a sequence brings, from which the kernel sizes its tiles."""
+    ``max_new`` (0: not known): the most tokens a sequence brings, from which the kernel sizes its tiles.
+    With ``unit`` and ``removal`` (float32 rows of n_heads * dim, n_t and e_t) the state instead loses what it answers
+    along n_t: S <- diag(decay_t) S - e_t (n_t^T S) + k_t v_t^T, both corrections from the state as the token found
+    it, and out_t = S^T q_t (no ``delta`` then)."""
+    if (unit is None) != (removal is None) or (unit is not None and delta):
+        raise KernelError("state_scan: unit and removal come together, and without the delta rule")
     n = out.shape[0]
     if out.shape != (n, n_heads * vdim) or out.dtype != torch.float32 or not out.is_contiguous():
         raise KernelError("state_scan: out must be float32 [T, heads * vdim]")
@@ -819,20 +834,27 @@ def state_scan(out, q, k, v, decay, beta, state, cu_seqlens, seq_slot, n_heads: 
     vp, vs = _columns(v, "v", n_heads * vdim)
     dp, ds = _columns(decay, "decay", n_heads * dim)
     bp, bs = _columns(beta, "beta", n_heads) if delta else (0, 0)
+    up, us = _columns(unit, "unit", n_heads * dim) if unit is not None else (0, 0)
+    rp, rs = _columns(removal, "removal", n_heads * dim) if removal is not None else (0, 0)
+    if unit is not None and (unit.shape[0] != n or removal.shape[0] != n):
+        raise KernelError("state_scan: one row a token is needed")
     n_seqs = seq_slot.numel()
     if cu_seqlens.numel() != n_seqs + 1:
         raise KernelError("state_scan: cu_seqlens must hold one entry more than seq_slot")
-    _check(_kernels().xrt_state_scan(_ptr(out, "out"), qp, qs, kp, ks, vp, vs, dp, ds, bp, bs, _ptr(state, "state"),
+    _check(_kernels().xrt_state_scan(_ptr(out, "out"), qp, qs, kp, ks, vp, vs, dp, ds, bp, bs, up, us, rp, rs, _ptr(state, "state"),
                                     _ptr(cu_seqlens, "cu_seqlens", torch.int32), _ptr(seq_slot, "seq_slot", torch.int32),
-                                    n_seqs, n_heads, n_qk_heads, dim, vdim, float(q_scale), 1 if delta else 0, int(max_new),
+                                    n_seqs, n_heads, n_qk_heads, dim, vdim, float(q_scale),
+                                    2 if unit is not None else (1 if delta else 0), int(max_new),
                                     _stream()),
            "state_scan")
 
 
-def short_conv(out, x, weight, state, cu_seqlens, seq_slot, max_new: int, act: str = "silu", bias=None) -> None:
+def short_conv(out, x, weight, state, cu_seqlens, seq_slot, max_new: int, act: str = "silu", bias=None, in_bias=None) -> None:
     """out[t, c] = act(bias[c] + sum_j weight[c, j] * x[t - (taps - 1) + j, c]) inside each sequence (no bias: 0); inputs before the
     step come from ``state`` [slots, taps - 1, channels] (zeros at a sequence's start), which is left holding
-    the sequence's last taps - 1 inputs.  x: float32 rows of at least ``channels`` columns; all float32."""
+    the sequence's last taps - 1 inputs.  x: float32 rows of at least ``channels`` columns; all float32.
+    ``in_bias`` (float32 [channels]): every input inside a sequence is x + in_bias (the bias of the product that gave
+    x, added here); the state holds such sums, and what stands before a sequence's start stays zero."""
     n, channels = out.shape
     taps = weight.shape[1]
     if weight.shape[0] != channels or x.shape[0] != n or out.dtype != torch.float32:
@@ -841,10 +863,10 @@ def short_conv(out, x, weight, state, cu_seqlens, seq_slot, max_new: int, act: s
         raise KernelError("short_conv: the state must be [slots, taps - 1, channels]")
     xp, xs = _columns(x, "x", channels)
     n_seqs = seq_slot.numel()
-    if bias is not None and bias.numel() != channels:
+    if any(b is not None and b.numel() != channels for b in (bias, in_bias)):
         raise KernelError("short_conv: one bias a channel is needed")
     _check(_kernels().xrt_short_conv(_ptr(out, "out"), xp, xs, _ptr(weight, "weight", torch.float32),
-                                    _ptr(bias, "bias", torch.float32),
+                                    _ptr(bias, "bias", torch.float32), _ptr(in_bias, "in_bias", torch.float32),
                                     _ptr(state if taps > 1 else None, "state", torch.float32),
                                     _ptr(cu_seqlens, "cu_seqlens", torch.int32), _ptr(seq_slot, "seq_slot", torch.int32),
                                     n_seqs, int(max_new), channels, taps, _ACTS[act], _stream()), "short_conv")
@@ -876,13 +898,15 @@ def unit_heads(x, n_heads: int, dim: int, eps: float, scaled_heads: int = 0, sca
 
 
 def head_norm_gate(y, o, weight, gate, n_heads: int, vdim: int, eps: float, act: str) -> None:
-    """y[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * act(gate[t, h]); o float32 [T, heads * vdim]."""
+    """y[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * act(gate[t, h]); o float32 [T, heads * vdim];
+    ``weight`` float32 [vdim] (shared by the heads) or [heads * vdim] (one a column of all heads)."""
     n = o.shape[0]
-    if y.shape != (n, n_heads * vdim) or o.shape != y.shape or weight.numel() != vdim or gate.shape[0] != n:
+    if y.shape != (n, n_heads * vdim) or o.shape != y.shape or weight.numel() not in (vdim, n_heads * vdim) or gate.shape[0] != n:
         raise KernelError("head_norm_gate: shapes do not fit")
     gp, gs = _columns(gate, "gate", n_heads * vdim)
     _check(_kernels().xrt_head_norm_gate(_ptr(y, "y"), _ptr(o, "o", torch.float32), _ptr(weight, "weight", torch.float32),
-                                        gp, gs, n, n_heads, vdim, float(eps), _ACTS[act], _code(y.dtype), _stream()),
+                                        gp, gs, n, n_heads, vdim, float(eps), _ACTS[act], _code(y.dtype),
+                                        1 if weight.numel() == n_heads * vdim and n_heads > 1 else 0, _stream()),
            "head_norm_gate")
 
 
@@ -973,7 +997,7 @@ def moe_route(ids, weights, logits, bias, top: int) -> None:
                                    _stream()), "moe_route")
 
 
-MOE_ACTS = {"gated_sigmoid": 0, "gelu": 1}
+MOE_ACTS = {"gated_sigmoid": 0, "gelu": 1, "gated_silu": 2}
 
 
 def _moe_act(act: str) -> int:
@@ -1032,15 +1056,25 @@ def moe_activation(act, gate_up, limit: float = 0.0, alpha: float = 0.0, kind: s
                                         _moe_act(kind), _code(act.dtype), _stream()), "moe_activation")
 
 
-def moe_route_scores(ids, weights, logits, top: int, groups: int = 1, keep: int = 1) -> None:
+def moe_route_scores(ids, weights, logits, top: int, groups: int = 1, keep: int = 1, scores: str = "softmax",
+                     correction=None, group_best: int = 1, normalize: bool = False, sum_eps: float = 0.0,
+                     scale: float = 1.0) -> None:
     """Routing by scores: softmax of ``logits`` over all experts; of ``groups`` equal groups of neighbouring experts
     only the ``keep`` whose best score is largest may be chosen from; ids int32 [T, top] are the ``top`` largest scores
-    among those and weights float32 [T, top] those scores as they are."""
+    among those and weights float32 [T, top] those scores as they are.
+    ``scores`` "sigmoid": every score is the sigmoid of its logit.  ``correction`` (float32 [experts]) is added to the
+    scores for every choice, of groups and of experts, but not for the weights.  ``group_best``: a group counts by the
+    sum of so many of its largest choice scores.  ``normalize``: the weights are divided by their sum + ``sum_eps``;
+    ``scale`` multiplies them."""
     n, experts = logits.shape
     if ids.shape != (n, top) or weights.shape != (n, top) or logits.dtype != torch.float32:
         raise KernelError("moe_route_scores: shapes do not fit")
+    if scores not in ("softmax", "sigmoid") or (correction is not None and correction.numel() != experts):
+        raise KernelError("moe_route_scores: scores are softmax or sigmoid, and a correction has one entry an expert")
     _check(_kernels().xrt_moe_route_scores(_ptr(ids, "ids", torch.int32), _ptr(weights, "weights", torch.float32),
-                                          _ptr(logits, "logits"), n, experts, int(top), int(groups), int(keep), _stream()),
+                                          _ptr(logits, "logits"), n, experts, int(top), int(groups), int(keep),
+                                          1 if scores == "sigmoid" else 0, _ptr(correction, "correction", torch.float32),
+                                          int(group_best), 1 if normalize else 0, float(sum_eps), float(scale), _stream()),
            "moe_route_scores")
 
 
@@ -1061,8 +1095,8 @@ def moe_grouped_product(out, a, w, offsets, n_experts: int, ff: int = 0, limit: 
     [experts * ff, k], no gate); without, out float32 [rows, n] from a [rows, k] and w [experts * n, k].
     ``offsets`` int32 [experts + 1] on the device."""
     rows, k = a.shape
-    first = (2 if act == "gelu" else 1) if ff > 0 else 0
-    n = (2 * ff if first == 1 else ff) if first else out.shape[1]
+    first = {"gelu": 2, "gated_silu": 3}.get(act, 1) if ff > 0 else 0
+    n = (ff if first == 2 else 2 * ff) if first else out.shape[1]
     _moe_act(act)
     if w.shape != (n_experts * n, k) or out.shape != (rows, ff if first else n) or offsets.numel() != n_experts + 1:
         raise KernelError("moe_grouped_product: shapes do not fit")
@@ -1133,14 +1167,15 @@ def qkv_heads_write(q_out, k_pool, v_pool, qkv, k_offset: int, v_offset: int, bi
                     eps: float, tok_slot, tok_pos, block_table, n_heads: int, n_kv_heads: int, head_dim: int,
                     v_keep=None, v_first=None, v_blend: float = 0.0, v_dim: int = 0, write_kv: bool = True,
                     q_norm_w=None, k_norm_w=None, whole_q: int = 0, whole_k: int = 0, cos_sin=None,
-                    pairing: str = "split_half") -> None:
+                    pairing: str = "split_half", v_unit: bool = False) -> None:
     """``qk_rope_kv_write`` without rotation for layers that add a bias a column of the q/k/v row (float32, laid out as
     the row), divide q and k heads by their root mean square without a weight (over ``norm_dim`` dims where the heads
     are laid out wider), keep the values in 32-bit (``v_keep`` [T, kv heads * v_dim]) and / or cache
     (1 - v_blend) v + v_blend v_first; ``v_dim`` (0: head_dim) is a head's true value size, at which v_keep and
     v_first hold the heads.  ``q_norm_w`` / ``k_norm_w`` with ``whole_q`` / ``whole_k`` > 0: an RMSNorm over the
     whole q (k) projection of a token, all heads at once, one weight a column of the projection as it is laid out, the
-    number being the divisor of the mean of squares; ``cos_sin`` and ``pairing`` as in ``qk_rope_kv_write``."""
+    number being the divisor of the mean of squares; ``cos_sin`` and ``pairing`` as in ``qk_rope_kv_write``.
+    ``v_unit``: every value head is divided by its root mean square over ``v_dim`` (``eps``, no weight) first."""
     n = qkv.shape[0]
     if pairing not in ("split_half", "interleaved"):
         raise KernelError(f"qkv_heads_write: pairing {pairing!r} is not split_half or interleaved")
@@ -1176,24 +1211,40 @@ def qkv_heads_write(q_out, k_pool, v_pool, qkv, k_offset: int, v_offset: int, bi
         _ptr(qkv, "qkv", torch.float32), qkv.shape[1], k_offset, v_offset, _ptr(bias, "bias", torch.float32),
         1 if unit_norm else 0, int(norm_dim), float(eps), _ptr(q_norm_w, "q_norm_w"), _ptr(k_norm_w, "k_norm_w"),
         _code(norm_dtype), int(whole_q), int(whole_k), _ptr(cos_sin, "cos_sin", torch.float32), rope_half,
-        1 if pairing == "interleaved" else 0, kp, ks, fp, fs, float(v_blend), true_v,
+        1 if pairing == "interleaved" else 0, kp, ks, fp, fs, float(v_blend), true_v, 1 if v_unit else 0,
         _ptr(tok_slot, "tok_slot", torch.int32), _ptr(tok_pos, "tok_pos", torch.int32),
         _ptr(block_table, "block_table", torch.int32), block_table.shape[1], n, n_heads, n_kv_heads, head_dim,
         1 if write_kv else 0, _code(q_out.dtype), _code(cache_dtype), _stream()), "qkv_heads_write")
 
 
-def rmsnorm_add(residual, y, weight, eps: float, copy=None) -> None:
-    """residual += RMSNorm(y) * weight, 32-bit; ``y`` float32 [T, width] or [parts, T, width] (added in index order
-    first); ``copy`` (optional, [T, width] in the compute dtype) receives the new residual as well."""
+def rmsnorm_add(residual, y, weight, eps: float, copy=None, factor: float = 1.0, part_scales=None, bias=None,
+                then=None) -> None:
+    """residual += factor * RMSNorm(y) * weight, 32-bit; ``y`` float32 [T, width] or [parts, T, width] (added in index
+    order first, part p times ``part_scales[p]`` (float32 on the device) where given, plus the row ``bias`` (float32
+    [width])); ``copy`` (optional, [T, width] in the compute dtype) receives the new residual as well; ``then`` =
+    (weight2, eps2, out2): out2 [T, width] receives RMSNorm(new residual) * weight2 (weight2 of ``weight``'s dtype)."""
     n, width = residual.shape
     parts = y.shape[0] if y.dim() == 3 else 1
     if tuple(y.shape[-2:]) != (n, width) or weight.numel() != width or residual.dtype != torch.float32:
         raise KernelError("rmsnorm_add: shapes do not fit")
     if copy is not None and tuple(copy.shape) != (n, width):
         raise KernelError("rmsnorm_add: the copy does not fit")
+    if part_scales is not None and part_scales.numel() != parts or bias is not None and bias.numel() != width:
+        raise KernelError("rmsnorm_add: one scale a part and one bias a column are needed")
+    then_w = then_out = None
+    then_eps = 0.0
+    if then is not None:
+        then_w, then_eps, then_out = then
+        if (tuple(then_out.shape) != (n, width) or then_w.numel() != width or then_w.dtype != weight.dtype
+                or (copy is not None and copy.dtype != then_out.dtype)):
+            raise KernelError("rmsnorm_add: the second norm does not fit")
+    side = copy if copy is not None else then_out
     _check(_kernels().xrt_rmsnorm_add(_ptr(residual, "residual"), _ptr(y, "y", torch.float32), n * width, parts,
                                      _ptr(weight, "weight"), _ptr(copy, "copy"), n, width, float(eps), _code(weight.dtype),
-                                     _code(copy.dtype if copy is not None else torch.float32), _stream()), "rmsnorm_add")
+                                     _code(side.dtype if side is not None else torch.float32),
+                                     _ptr(part_scales, "part_scales", torch.float32), _ptr(bias, "bias", torch.float32),
+                                     float(factor), _ptr(then_w, "then weight"), _ptr(then_out, "then out"),
+                                     float(then_eps), _stream()), "rmsnorm_add")
 
 
 def cast_rows(out, x) -> None:
@@ -1245,3 +1296,71 @@ def head_product(out, out_head: int, out_off: int, x, x_head: int, x_off: int, w
     _check(_kernels().xrt_head_product(_ptr(out, "out"), out.stride(0), int(out_head), int(out_off), _ptr(x, "x"),
                                       x.stride(0), int(x_head), int(x_off), _ptr(w, "w"), t, n_heads, n, k,
                                       _code(x.dtype), _code(w.dtype), _code(out.dtype), _stream()), "head_product")
+
+
+# ---------------------------------------------------------------------------------------------------
+# Token shift, the row that a pass over a stretch of layers begins with, and the gates of the scan's removal form
+def rmsnorm_shift(out, x, weight, shift, state, ctx_arrays, eps: float, single_tokens: bool) -> None:
+    """out[t] = n_t + (n_(t-1) - n_t) * shift with n = RMSNorm(x) * weight in 32-bit (csrc/token_shift.cu); n_(t-1) is
+    zero at a sequence's start and comes from ``state`` float32 [slots, width] for a step's first token, and the state
+    is left holding the n of each sequence's last token.  ``ctx_arrays`` = (tok_slot, tok_pos, cu_seqlens, seq_slot).
+    ``single_tokens``: every sequence of the step brings one token (one launch instead of two)."""
+    n, width = x.shape
+    tok_slot, tok_pos, cu_seqlens, seq_slot = ctx_arrays
+    if (out.shape != x.shape or x.dtype != torch.float32 or weight.numel() != width or shift.numel() != width
+            or state.dim() != 2 or state.shape[1] != width or tok_slot.numel() != n or tok_pos.numel() != n
+            or cu_seqlens.numel() != seq_slot.numel() + 1 or not x.is_contiguous() or not state.is_contiguous()):
+        raise KernelError("rmsnorm_shift: shapes do not fit")
+    _check(_kernels().xrt_rmsnorm_shift(_ptr(out, "out"), _ptr(x, "x"), _ptr(weight, "weight"),
+                                       _ptr(shift, "shift", torch.float32), _ptr(state, "state", torch.float32),
+                                       _ptr(tok_slot, "tok_slot", torch.int32), _ptr(tok_pos, "tok_pos", torch.int32),
+                                       _ptr(cu_seqlens, "cu_seqlens", torch.int32), _ptr(seq_slot, "seq_slot", torch.int32),
+                                       seq_slot.numel(), n, width, float(eps), 1 if single_tokens else 0,
+                                       _code(weight.dtype), _code(out.dtype), _stream()), "rmsnorm_shift")
+    if not single_tokens:
+        add_launches(1)
+
+
+def add_row(x, row) -> None:
+    """x[t] += row in place; x float32 [T, width], row [width]."""
+    if x.dim() != 2 or x.dtype != torch.float32 or row.numel() != x.shape[1] or not x.is_contiguous():
+        raise KernelError("add_row: shapes do not fit")
+    _check(_kernels().xrt_add_row(_ptr(x, "x"), _ptr(row, "row"), x.shape[0], x.shape[1], _code(row.dtype), _stream()),
+           "add_row")
+
+
+def removal_gates(decay, decay_bias, removal, removal_bias, unit, k, n_heads: int, dim: int, rate: float,
+                  unit_eps: float) -> None:
+    """From raw products, per head of ``dim`` channels: decay <- exp(-rate * sigmoid(decay + decay_bias)) in place;
+    unit = k / sqrt(sum(k^2) + unit_eps); removal <- sigmoid(removal + removal_bias) * unit in place.  All float32
+    rows of at least n_heads * dim columns (slices of wider rows allowed); the biases float32 [n_heads * dim]."""
+    n = k.shape[0]
+    width = n_heads * dim
+    dp, ds = _columns(decay, "decay", width)
+    rp, rs = _columns(removal, "removal", width)
+    up, us = _columns(unit, "unit", width)
+    kp, ks = _columns(k, "k", width)
+    if any(t.shape[0] != n for t in (decay, removal, unit)) or decay_bias.numel() != width or removal_bias.numel() != width:
+        raise KernelError("removal_gates: shapes do not fit")
+    _check(_kernels().xrt_removal_gates(dp, ds, _ptr(decay_bias, "decay_bias", torch.float32), rp, rs,
+                                       _ptr(removal_bias, "removal_bias", torch.float32), up, us, kp, ks, n, n_heads, dim,
+                                       float(rate), float(unit_eps), _stream()), "removal_gates")
+
+
+def act_cast(out, x, act: str) -> None:
+    """out = act(x) in out's dtype; x float32 rows of at least out's width (a slice of wider rows allowed); ``act``
+    "none", "silu", "sigmoid" or "tanh"."""
+    n, width = out.shape
+    xp, xs = _columns(x, "x", width)
+    if x.shape[0] != n:
+        raise KernelError("act_cast: shapes do not fit")
+    _check(_kernels().xrt_act_cast(_ptr(out, "out"), xp, xs, n, width, _ACTS[act], _code(out.dtype), _stream()), "act_cast")
+
+
+def add_scaled_parts(residual, parts, scales) -> None:
+    """residual += sum_p scales[p] * parts[p]; residual float32 [T, width], parts float32 [n, T, width], scales float32 [n]."""
+    if parts.dim() != 3 or tuple(parts.shape[1:]) != tuple(residual.shape) or scales.numel() != parts.shape[0]:
+        raise KernelError("add_scaled_parts: shapes do not fit")
+    _check(_kernels().xrt_add_scaled_parts(_ptr(residual, "residual", torch.float32), _ptr(parts, "parts", torch.float32),
+                                          _ptr(scales, "scales", torch.float32), residual.numel(), parts.shape[0],
+                                          _stream()), "add_scaled_parts")

@@ -64,6 +64,8 @@ __global__ void rotation_table_kernel(float2* __restrict__ cos_sin, const int* _
 //   v_first    the cached value is (1 - v_blend) v + v_blend v_first[token], v_first rows of v_first_stride floats
 //   v_dim      the value size of a head in v_keep and v_first, which hold the heads at their true size whatever
 //              size the layer's heads are laid out at (0: head_dim)
+//   v_unit     every value head is divided by its root mean square over v_dim (eps of the layer, no weight) before
+//              it is kept, blended or cached
 //   whole_q, whole_k   > 0: the RMSNorm of q (of k) runs over the WHOLE projection, all heads of a token at once, with
 //              one weight a column ([heads * head_dim], laid out as the heads are); the number is the divisor of the
 //              mean of squares (the projection's true size, which is smaller than heads * head_dim where the heads
@@ -80,6 +82,7 @@ struct HeadExtras {
   int v_first_stride = 0;
   float v_blend = 0.f;
   int v_dim = 0;
+  int v_unit = 0;
 };
 
 // One warp per (token, head) among [q heads | k heads | v heads].  MAX_PER_LANE * 32 >= head_dim.
@@ -158,6 +161,11 @@ __global__ void qk_rope_kv_write_kernel(
   }
   if (kind == 2) {
     const int v_dim = ex.v_dim > 0 ? ex.v_dim : head_dim;
+    if (ex.v_unit) {  // dims beyond v_dim hold zeros (zero rows of the matrix, no bias there)
+      const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)v_dim + eps);
+#pragma unroll
+      for (int j = 0; j < MAX_PER_LANE; ++j) v[j] *= inv;
+    }
 #pragma unroll
     for (int j = 0; j < MAX_PER_LANE; ++j) {
       const int d = lane + 32 * j;
@@ -359,7 +367,7 @@ static int qk_rope_kv_write(void* q_out, void* k_pool, void* v_pool, const float
                             int n_heads, int n_kv_heads, int head_dim, int write_kv, int interleaved,
                             int norm_dtype, int q_dtype, int cache_dtype, const xrt::HeadExtras& ex, cudaStream_t stream) {
   const bool plain = ex.bias == nullptr && !ex.unit_norm && ex.norm_dim == 0 && ex.v_keep == nullptr && ex.v_first == nullptr &&
-                     ex.whole_q == 0 && ex.whole_k == 0;
+                     ex.whole_q == 0 && ex.whole_k == 0 && !ex.v_unit;
   if (n_tokens < 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0) return XRT_ERR_ARGUMENT;
   if (head_dim > 256 || 2 * rope_half > head_dim) return XRT_ERR_UNSUPPORTED;
   if (write_kv && (q_norm_w == nullptr) != (k_norm_w == nullptr)) return XRT_ERR_ARGUMENT;  // a layer that reads another's keys norms only q
@@ -416,10 +424,12 @@ XRT_EXPORT int xrt_qkv_heads_write(void* q_out, void* k_pool, void* v_pool, cons
                                    const void* q_norm_w, const void* k_norm_w, int norm_dtype, int whole_q, int whole_k,
                                    const float* cos_sin, int rope_half, int interleaved,
                                    float* v_keep, int v_keep_stride, const float* v_first, int v_first_stride,
-                                   float v_blend, int v_dim, const int* tok_slot, const int* tok_pos, const int* block_table,
+                                   float v_blend, int v_dim, int v_unit, const int* tok_slot, const int* tok_pos,
+                                   const int* block_table,
                                    int max_blocks, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int write_kv,
                                    int q_dtype, int cache_dtype, cudaStream_t stream) {
   xrt::HeadExtras ex;
+  ex.v_unit = v_unit;
   ex.bias = bias;
   ex.unit_norm = unit_norm;
   ex.norm_dim = norm_dim;

@@ -5,8 +5,14 @@
 //   state scan        S_t = diag(a_t) S_(t-1) + k_t u_t^T,   o_t = S_t^T q_t
 //                     plain:       u_t = v_t                                   (gated linear attention)
 //                     delta rule:  u_t = b_t (v_t - (diag(a_t) S_(t-1))^T k_t) (the read-out sees the write)
+//                     removal:     S_t = diag(a_t) S_(t-1) - e_t (n_t^T S_(t-1)) + k_t v_t^T, with two more vectors a
+//                                  token and head, n_t (a unit key) and e_t (a removal rate times n_t); the decay and
+//                                  the removal both read the state as the token found it
+//   removal gates     from raw products: a = exp(-rate * sigmoid(z + bias)), n = k / sqrt(sum(k^2) + eps) per head,
+//                     e = sigmoid(y + bias) * n
 //   short convolution y_t = act(bias[c] + sum_j w[c, j] x_(t - (taps - 1) + j)) per channel (the bias is optional), zeros before a sequence's
-//                     start; the last taps - 1 inputs of a sequence are its state
+//                     start; the last taps - 1 inputs of a sequence are its state; with `in_bias` every input inside
+//                     the sequence is x + in_bias[c] (a product's bias, added here), and the state holds them so
 //   decays            a = sigmoid(z + bias)^(1 / tau)   or   a = exp(-exp(A) softplus(z + bias))
 //   unit heads        x / sqrt(sum(x^2) + eps) * scale per head
 //   head norm + gate  o / sqrt(mean(o^2) + eps) * w * act(g) per head
@@ -19,8 +25,8 @@ namespace xrt {
 
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplusf_(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
-__device__ __forceinline__ float activate(float z, int act) {  // 0 none, 1 silu, 2 sigmoid
-  return act == 1 ? z * sigmoidf_(z) : (act == 2 ? sigmoidf_(z) : z);
+__device__ __forceinline__ float activate(float z, int act) {  // 0 none, 1 silu, 2 sigmoid, 3 tanh
+  return act == 1 ? z * sigmoidf_(z) : (act == 2 ? sigmoidf_(z) : (act == 3 ? tanhf(z) : z));
 }
 
 // ------------------------------------------------------------------------------------------ the scan
@@ -45,6 +51,8 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 struct ScanArgs {
   float* out;
   const float *q, *k, *v, *decay, *beta;
+  const float *unit, *removal;  // MODE 2: n_t and e_t, rows of heads * dim
+  int unit_stride, removal_stride;
   int q_stride, k_stride, v_stride, decay_stride, beta_stride;
   float* state;
   const int *cu_seqlens, *seq_slot;
@@ -56,14 +64,17 @@ struct ScanArgs {
 // VEC: 16-byte copies (dim, vdim, cols and every row stride are multiples of 4 floats, every base 16-byte aligned).
 // C2: value columns a lane holds (C2 * R state registers): what a lane reads of q, k and a serves C2 columns, and
 // the kernel is bound by what its warps ask of shared memory.
-template <int R, int C2, bool DELTA, bool VEC>
+// MODE 0: plain, 1: delta rule, 2: removal along a unit key (two more vectors in a stage).
+template <int R, int C2, int MODE, bool VEC>
 __global__ void __launch_bounds__(128) state_scan_kernel(const ScanArgs a) {
+  constexpr bool DELTA = MODE == 1;
+  constexpr int NVEC = MODE == 2 ? 5 : 3;  // vectors of `padded` floats a token in a stage
   extern __shared__ float4 tile4[];
   float* tile = reinterpret_cast<float*>(tile4);
   pdl_trigger();
   const int parts = a.parts, cols = a.cols, TT = a.tile_tokens, dim = a.dim, vdim = a.vdim;
   const int padded = parts * R;
-  // a stage: q | k | a, each [TT][padded]; then v [TT][cols]; then b [TT] (regions of whole 16 bytes)
+  // a stage: q | k | a (| n | e), each [TT][padded]; then v [TT][cols]; then b [TT] (regions of whole 16 bytes)
   const int vec_floats = TT * padded, v_floats = (TT * cols + 3) & ~3;
   if (padded != dim || vdim % cols != 0)  // rows and columns beyond the head's stay zero
     for (int e = threadIdx.x; e < 2 * a.stage_floats; e += blockDim.x) tile[e] = 0.f;
@@ -83,7 +94,7 @@ __global__ void __launch_bounds__(128) state_scan_kernel(const ScanArgs a) {
     float* sq = tile + stage * a.stage_floats;
     float* sk = sq + vec_floats;
     float* sa = sk + vec_floats;
-    float* sv = sa + vec_floats;
+    float* sv = sq + NVEC * vec_floats;
     float* sb = sv + v_floats;
     const int nt = min(TT, end - t0);
     const int per = dim / E;
@@ -94,6 +105,10 @@ __global__ void __launch_bounds__(128) state_scan_kernel(const ScanArgs a) {
       cp_async<B>(sq + at, a.q + t * a.q_stride + qh * dim + d);
       cp_async<B>(sk + at, a.k + t * a.k_stride + qh * dim + d);
       cp_async<B>(sa + at, a.decay + t * a.decay_stride + h * dim + d);
+      if (MODE == 2) {
+        cp_async<B>(sa + vec_floats + at, a.unit + t * a.unit_stride + h * dim + d);
+        cp_async<B>(sa + 2 * vec_floats + at, a.removal + t * a.removal_stride + h * dim + d);
+      }
     }
     const int vper = cols / E;
     for (int e = threadIdx.x; e < nt * vper; e += blockDim.x) {
@@ -142,8 +157,8 @@ __global__ void __launch_bounds__(128) state_scan_kernel(const ScanArgs a) {
     const float* sq = tile + stage * a.stage_floats;
     const float* sk = sq + vec_floats;
     const float* sa = sk + vec_floats;
-    const float* sv = sa + vec_floats;
-    float* sb = tile + stage * a.stage_floats + 3 * vec_floats + v_floats;
+    const float* sv = sq + NVEC * vec_floats;
+    float* sb = tile + stage * a.stage_floats + NVEC * vec_floats + v_floats;
     if (DELTA)  // b = sigmoid(raw), once a tile, by the thread whose own copy brought the raw value
       for (int tt = threadIdx.x; tt < nt; tt += blockDim.x) sb[tt] = sigmoidf_(sb[tt]);
     __syncthreads();
@@ -188,6 +203,43 @@ __global__ void __launch_bounds__(128) state_scan_kernel(const ScanArgs a) {
         for (int c = 0; c < C2; ++c)
 #pragma unroll
           for (int i = 0; i < R / 2; ++i) S[c][i] = __ffma2_rn(kr[i], make_float2(u[c], u[c]), S[c][i]);
+      } else if (MODE == 2) {
+        // what the state answers along the unit key, from the state as the token found it
+        const float4* pn = reinterpret_cast<const float4*>(sa + vec_floats + tt * padded) + part;
+        const float4* pe = reinterpret_cast<const float4*>(sa + 2 * vec_floats + tt * padded) + part;
+        float2 seen[C2][2];
+#pragma unroll
+        for (int c = 0; c < C2; ++c) seen[c][0] = seen[c][1] = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < R; i += 4) {
+          const float4 n = pn[(i / 4) * parts];
+#pragma unroll
+          for (int c = 0; c < C2; ++c) {
+            seen[c][0] = __ffma2_rn(S[c][i / 2], make_float2(n.x, n.y), seen[c][0]);
+            seen[c][1] = __ffma2_rn(S[c][i / 2 + 1], make_float2(n.z, n.w), seen[c][1]);
+          }
+        }
+        float gone[C2];
+#pragma unroll
+        for (int c = 0; c < C2; ++c) {
+          float total = (seen[c][0].x + seen[c][0].y) + (seen[c][1].x + seen[c][1].y);
+          for (int o = 1; o < parts; o <<= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+          gone[c] = -total;
+        }
+#pragma unroll
+        for (int i = 0; i < R; i += 4) {
+          const float4 d = pa[(i / 4) * parts];
+          const float4 e = pe[(i / 4) * parts];
+#pragma unroll
+          for (int c = 0; c < C2; ++c) {
+            const float2 uu = make_float2(u[c], u[c]), gg = make_float2(gone[c], gone[c]);
+            // diag(a) S - e (n^T S) + k v^T, the two corrections first
+            const float2 lo = __ffma2_rn(make_float2(e.x, e.y), gg, __fmul2_rn(kr[i / 2], uu));
+            const float2 hi = __ffma2_rn(make_float2(e.z, e.w), gg, __fmul2_rn(kr[i / 2 + 1], uu));
+            S[c][i / 2] = __ffma2_rn(S[c][i / 2], make_float2(d.x, d.y), lo);
+            S[c][i / 2 + 1] = __ffma2_rn(S[c][i / 2 + 1], make_float2(d.z, d.w), hi);
+          }
+        }
       } else {
 #pragma unroll
         for (int i = 0; i < R; i += 4) {
@@ -245,7 +297,7 @@ __global__ void __launch_bounds__(128) state_scan_kernel(const ScanArgs a) {
 // come from the sequence's state [slot][taps - 1][channels] (the newest last).
 __global__ void short_conv_kernel(float* __restrict__ out, const float* __restrict__ x, int x_stride,
                                   const float* __restrict__ w, const float* __restrict__ bias,
-                                  const float* __restrict__ state,
+                                  const float* __restrict__ in_bias, const float* __restrict__ state,
                                   const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot, int channels,
                                   int taps, int tile_tokens, int act) {
   pdl_trigger();
@@ -258,11 +310,12 @@ __global__ void short_conv_kernel(float* __restrict__ out, const float* __restri
   const int l1 = min(len, l0 + tile_tokens);
   const float* st = state + (size_t)slot * (taps - 1) * channels;
   for (int c = blockIdx.z * blockDim.x + threadIdx.x; c < channels; c += gridDim.z * blockDim.x) {
+    const float ib = in_bias != nullptr ? in_bias[c] : 0.f;
     for (int l = l0; l < l1; ++l) {
       float acc = bias != nullptr ? bias[c] : 0.f;
       for (int jj = 0; jj < taps; ++jj) {
         const int src = l - (taps - 1) + jj;  // local index of the input under tap jj
-        const float xv = src >= 0 ? x[(size_t)(begin + src) * x_stride + c] : st[(size_t)(taps - 1 + src) * channels + c];
+        const float xv = src >= 0 ? x[(size_t)(begin + src) * x_stride + c] + ib : st[(size_t)(taps - 1 + src) * channels + c];
         acc = fmaf(w[c * taps + jj], xv, acc);
       }
       out[(size_t)(begin + l) * channels + c] = activate(acc, act);
@@ -273,6 +326,7 @@ __global__ void short_conv_kernel(float* __restrict__ out, const float* __restri
 // The state after the step: the last taps - 1 inputs of the sequence (older ones shift out).
 template <int MAX_KEEP>
 __global__ void short_conv_state_kernel(float* __restrict__ state, const float* __restrict__ x, int x_stride,
+                                        const float* __restrict__ in_bias,
                                         const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
                                         int channels, int taps) {
   pdl_trigger();
@@ -289,7 +343,8 @@ __global__ void short_conv_state_kernel(float* __restrict__ state, const float* 
     for (int i = 0; i < MAX_KEEP; ++i) {
       if (i < keep) {
         const int src = len - keep + i;
-        next[i] = src >= 0 ? x[(size_t)(begin + src) * x_stride + c] : st[(size_t)(keep + src) * channels + c];
+        next[i] = src >= 0 ? x[(size_t)(begin + src) * x_stride + c] + (in_bias != nullptr ? in_bias[c] : 0.f)
+                           : st[(size_t)(keep + src) * channels + c];
       }
     }
 #pragma unroll
@@ -328,11 +383,41 @@ __global__ void unit_heads_kernel(float* __restrict__ x, int stride, int n_token
   for (int d = lane; d < dim; d += 32) p[d] *= f;
 }
 
+// One warp a (token, head): the three vectors that the removal form of the scan reads beside q, k and v.
+//   decay[c]   <- exp(-rate * sigmoid(decay[c] + decay_bias[c]))            (in place over the raw product)
+//   unit[c]     = k[c] / sqrt(sum over the head of k^2 + unit_eps)
+//   removal[c] <- sigmoid(removal[c] + removal_bias[c]) * unit[c]            (in place over the raw product)
+__global__ void removal_gates_kernel(float* __restrict__ decay, int decay_stride, const float* __restrict__ decay_bias,
+                                     float* __restrict__ removal, int removal_stride,
+                                     const float* __restrict__ removal_bias, float* __restrict__ unit, int unit_stride,
+                                     const float* __restrict__ k, int k_stride, int n_tokens, int n_heads, int dim,
+                                     float rate, float unit_eps) {
+  pdl_trigger();
+  pdl_wait();
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= n_tokens * n_heads) return;
+  const int t = warp / n_heads, head = warp - t * n_heads;
+  const float* kp = k + (size_t)t * k_stride + head * dim;
+  float sum = 0.f;
+  for (int d = lane; d < dim; d += 32) sum = fmaf(kp[d], kp[d], sum);
+  const float inv = 1.0f / sqrtf(warp_sum(sum) + unit_eps);
+  float* dp = decay + (size_t)t * decay_stride + head * dim;
+  float* rp = removal + (size_t)t * removal_stride + head * dim;
+  float* up = unit + (size_t)t * unit_stride + head * dim;
+  for (int d = lane; d < dim; d += 32) {
+    const int c = head * dim + d;
+    const float n = kp[d] * inv;
+    dp[d] = expf(-rate * sigmoidf_(dp[d] + decay_bias[c]));
+    rp[d] = sigmoidf_(rp[d] + removal_bias[c]) * n;
+    up[d] = n;
+  }
+}
+
 // One warp a (token, head): y = o / sqrt(mean(o^2) + eps) * w * act(gate).
 template <typename TO>
 __global__ void head_norm_gate_kernel(TO* __restrict__ y, const float* __restrict__ o, const float* __restrict__ w,
                                       const float* __restrict__ gate, int gate_stride, int n_tokens, int n_heads,
-                                      int vdim, float eps, int act) {
+                                      int vdim, float eps, int act, int w_per_head) {
   pdl_trigger();
   pdl_wait();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
@@ -345,7 +430,8 @@ __global__ void head_norm_gate_kernel(TO* __restrict__ y, const float* __restric
   sum = warp_sum(sum);
   const float inv = 1.0f / sqrtf(sum / (float)vdim + eps);
   TO* dst = y + ((size_t)t * n_heads + head) * vdim;
-  for (int d = lane; d < vdim; d += 32) dst[d] = from_float<TO>((p[d] * inv) * w[d] * activate(g[d], act));
+  const float* wh = w + (w_per_head ? head * vdim : 0);  // one weight a column of all heads, or one shared by the heads
+  for (int d = lane; d < vdim; d += 32) dst[d] = from_float<TO>((p[d] * inv) * wh[d] * activate(g[d], act));
 }
 
 // x[t, c] *= act(gate[t, c]) in place.
@@ -410,6 +496,31 @@ __global__ void concat_cast_kernel(TO* __restrict__ out, const float* __restrict
   }
 }
 
+// out[t, c] = act(x[t, c]) in the compute dtype; x rows may be slices of wider rows.
+template <typename TO>
+__global__ void act_cast_kernel(TO* __restrict__ out, const float* __restrict__ x, int x_stride, int n_tokens, int width,
+                                int act) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t total = (size_t)n_tokens * width;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / width, c = i - t * width;
+    out[i] = from_float<TO>(activate(x[t * x_stride + c], act));
+  }
+}
+
+// residual[t, c] += sum_p scales[p] * parts[p][t, c], the parts in index order.
+__global__ void add_scaled_parts_kernel(float* __restrict__ residual, const float* __restrict__ parts,
+                                        const float* __restrict__ scales, size_t total, int n_parts) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    float sum = 0.f;
+    for (int p = 0; p < n_parts; ++p) sum = fmaf(parts[(size_t)p * total + i], scales[p], sum);
+    residual[i] += sum;
+  }
+}
+
 // x <- cap * tanh(x * scale / cap), or x * scale without a cap.
 __global__ void scale_softcap_kernel(float* __restrict__ x, size_t total, float scale, float cap) {
   pdl_trigger();
@@ -434,9 +545,12 @@ static int scan_rows_per_lane(int dim) { return dim <= 32 ? 8 : (dim <= 64 ? 16 
 
 XRT_EXPORT int xrt_state_scan(float* out, const float* q, int q_stride, const float* k, int k_stride, const float* v,
                               int v_stride, const float* decay, int decay_stride, const float* beta, int beta_stride,
+                              const float* unit, int unit_stride, const float* removal, int removal_stride,
                               float* state, const int* cu_seqlens, const int* seq_slot, int n_seqs, int n_heads,
-                              int n_qk_heads, int dim, int vdim, float q_scale, int delta, int max_new,
+                              int n_qk_heads, int dim, int vdim, float q_scale, int mode, int max_new,
                               cudaStream_t stream) {
+  const bool delta = mode == 1;
+  if (mode < 0 || mode > 2 || (mode == 2 && (unit == nullptr || removal == nullptr))) return XRT_ERR_ARGUMENT;
   if (max_new < 1) max_new = 1 << 30;
   if (n_seqs < 0 || n_heads <= 0 || n_qk_heads <= 0 || n_heads % n_qk_heads || dim <= 0 || vdim <= 0)
     return XRT_ERR_ARGUMENT;
@@ -457,7 +571,8 @@ XRT_EXPORT int xrt_state_scan(float* out, const float* q, int q_stride, const fl
   if (groups * parts < 32) groups = 32 / parts;
   const int cols = groups * per_lane;
   const int padded = parts * R;
-  auto stage_floats = [&](int tt) { return 3 * tt * padded + ((tt * cols + 3) & ~3) + ((tt + 3) & ~3); };
+  const int n_vec = mode == 2 ? 5 : 3;
+  auto stage_floats = [&](int tt) { return n_vec * tt * padded + ((tt * cols + 3) & ~3) + ((tt + 3) & ~3); };
   int tile_tokens = 16;
   while (tile_tokens > 1 && 2 * (size_t)stage_floats(tile_tokens) * sizeof(float) > 44 * 1024) tile_tokens >>= 1;
   // no more than the step's longest sequence brings: a decode step's blocks are small and many fit a multiprocessor
@@ -465,19 +580,23 @@ XRT_EXPORT int xrt_state_scan(float* out, const float* q, int q_stride, const fl
   const size_t smem = 2 * (size_t)stage_floats(tile_tokens) * sizeof(float);
   if (smem > 48 * 1024) return XRT_ERR_UNSUPPORTED;
   const bool vec = dim % 4 == 0 && vdim % 4 == 0 && cols % 4 == 0 && q_stride % 4 == 0 && k_stride % 4 == 0 &&
-                   v_stride % 4 == 0 && decay_stride % 4 == 0 &&
-                   (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)decay | (uintptr_t)state) & 15) == 0;
-  xrt::ScanArgs a = {out, q, k, v, decay, beta, q_stride, k_stride, v_stride, decay_stride, beta_stride, state,
+                   v_stride % 4 == 0 && decay_stride % 4 == 0 && unit_stride % 4 == 0 && removal_stride % 4 == 0 &&
+                   (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)decay | (uintptr_t)state |
+                     (uintptr_t)unit | (uintptr_t)removal) & 15) == 0;
+  xrt::ScanArgs a = {out, q, k, v, decay, beta, unit, removal, unit_stride, removal_stride,
+                     q_stride, k_stride, v_stride, decay_stride, beta_stride, state,
                      cu_seqlens, seq_slot, n_heads, n_heads / n_qk_heads, dim, vdim, q_scale, parts, cols, tile_tokens,
                      stage_floats(tile_tokens)};
   const dim3 grid(n_seqs, n_heads, (vdim + cols - 1) / cols), block(parts * groups);
 #define XRT_SCAN(RR, CC, DD, VV) xrt::launch_kernel(xrt::state_scan_kernel<RR, CC, DD, VV>, grid, block, smem, stream, a)
 #define XRT_SCAN_R(RR, CC)                                     \
   do {                                                         \
-    if (delta && vec) XRT_SCAN(RR, CC, true, true);            \
-    else if (delta) XRT_SCAN(RR, CC, true, false);             \
-    else if (vec) XRT_SCAN(RR, CC, false, true);               \
-    else XRT_SCAN(RR, CC, false, false);                       \
+    if (mode == 2 && vec) XRT_SCAN(RR, CC, 2, true);           \
+    else if (mode == 2) XRT_SCAN(RR, CC, 2, false);            \
+    else if (delta && vec) XRT_SCAN(RR, CC, 1, true);          \
+    else if (delta) XRT_SCAN(RR, CC, 1, false);                \
+    else if (vec) XRT_SCAN(RR, CC, 0, true);                   \
+    else XRT_SCAN(RR, CC, 0, false);                           \
   } while (0)
   if (R == 8) XRT_SCAN_R(8, 1);
   else if (R == 16) XRT_SCAN_R(16, 1);
@@ -488,8 +607,8 @@ XRT_EXPORT int xrt_state_scan(float* out, const float* q, int q_stride, const fl
   return xrt::launch_status();
 }
 
-XRT_EXPORT int xrt_short_conv(float* out, const float* x, int x_stride, const float* w, const float* bias, float* state,
-                              const int* cu_seqlens, const int* seq_slot, int n_seqs, int max_new, int channels,
+XRT_EXPORT int xrt_short_conv(float* out, const float* x, int x_stride, const float* w, const float* bias,
+                              const float* in_bias, float* state, const int* cu_seqlens, const int* seq_slot, int n_seqs, int max_new, int channels,
                               int taps, int act, cudaStream_t stream) {
   if (n_seqs < 0 || channels <= 0 || taps < 1 || max_new < 0) return XRT_ERR_ARGUMENT;
   if (taps > 9 || n_seqs > 65535) return XRT_ERR_UNSUPPORTED;
@@ -499,11 +618,11 @@ XRT_EXPORT int xrt_short_conv(float* out, const float* x, int x_stride, const fl
   const int channel_blocks = (channels + threads - 1) / threads;
   xrt::launch_kernel(xrt::short_conv_kernel,
                      dim3(n_seqs, (max_new + tile_tokens - 1) / tile_tokens, channel_blocks < 65535 ? channel_blocks : 65535),
-                     dim3(threads), 0, stream, out, x, x_stride, w, bias, (const float*)state, cu_seqlens, seq_slot, channels, taps, tile_tokens,
+                     dim3(threads), 0, stream, out, x, x_stride, w, bias, in_bias, (const float*)state, cu_seqlens, seq_slot, channels, taps, tile_tokens,
                      act);
   if (taps > 1)
     xrt::launch_kernel(xrt::short_conv_state_kernel<8>, dim3(n_seqs, (channels + 255) / 256), dim3(256), 0, stream, state,
-                       x, x_stride, cu_seqlens, seq_slot, channels, taps);
+                       x, x_stride, in_bias, cu_seqlens, seq_slot, channels, taps);
   return xrt::launch_status();
 }
 
@@ -528,15 +647,28 @@ XRT_EXPORT int xrt_unit_heads(float* x, int stride, int n_tokens, int n_heads, i
   return xrt::launch_status();
 }
 
+XRT_EXPORT int xrt_removal_gates(float* decay, int decay_stride, const float* decay_bias, float* removal,
+                                 int removal_stride, const float* removal_bias, float* unit, int unit_stride,
+                                 const float* k, int k_stride, int n_tokens, int n_heads, int dim, float rate,
+                                 float unit_eps, cudaStream_t stream) {
+  if (n_tokens < 0 || n_heads <= 0 || dim <= 0) return XRT_ERR_ARGUMENT;
+  if (n_tokens == 0) return XRT_OK;
+  const size_t warps = (size_t)n_tokens * n_heads;
+  xrt::launch_kernel(xrt::removal_gates_kernel, dim3((unsigned)((warps + 7) / 8)), dim3(256), 0, stream, decay,
+                     decay_stride, decay_bias, removal, removal_stride, removal_bias, unit, unit_stride, k, k_stride,
+                     n_tokens, n_heads, dim, rate, unit_eps);
+  return xrt::launch_status();
+}
+
 XRT_EXPORT int xrt_head_norm_gate(void* y, const float* o, const float* w, const float* gate, int gate_stride,
                                   int n_tokens, int n_heads, int vdim, float eps, int act, int out_dtype,
-                                  cudaStream_t stream) {
+                                  int w_per_head, cudaStream_t stream) {
   if (n_tokens < 0 || n_heads <= 0 || vdim <= 0 || gate_stride < n_heads * vdim) return XRT_ERR_ARGUMENT;
   if (n_tokens == 0) return XRT_OK;
   const size_t warps = (size_t)n_tokens * n_heads;
   XRT_DISPATCH_DTYPE(out_dtype, TO, {
     xrt::launch_kernel(xrt::head_norm_gate_kernel<TO>, dim3((unsigned)((warps + 7) / 8)), dim3(256), 0, stream, (TO*)y, o,
-                       w, gate, gate_stride, n_tokens, n_heads, vdim, eps, act);
+                       w, gate, gate_stride, n_tokens, n_heads, vdim, eps, act, w_per_head);
   });
   return xrt::launch_status();
 }
@@ -574,6 +706,26 @@ XRT_EXPORT int xrt_concat_cast(void* out, const float* a, const float* b, int n_
     xrt::launch_kernel(xrt::concat_cast_kernel<TO>, dim3(xrt::grid_for((size_t)n_tokens * 2 * width, 256)), dim3(256), 0,
                        stream, (TO*)out, a, b, n_tokens, width);
   });
+  return xrt::launch_status();
+}
+
+XRT_EXPORT int xrt_act_cast(void* out, const float* x, int x_stride, int n_tokens, int width, int act, int out_dtype,
+                            cudaStream_t stream) {
+  if (n_tokens < 0 || width <= 0 || x_stride < width) return XRT_ERR_ARGUMENT;
+  if (n_tokens == 0) return XRT_OK;
+  XRT_DISPATCH_DTYPE(out_dtype, TO, {
+    xrt::launch_kernel(xrt::act_cast_kernel<TO>, dim3(xrt::grid_for((size_t)n_tokens * width, 256)), dim3(256), 0, stream,
+                       (TO*)out, x, x_stride, n_tokens, width, act);
+  });
+  return xrt::launch_status();
+}
+
+XRT_EXPORT int xrt_add_scaled_parts(float* residual, const float* parts, const float* scales, long long total, int n_parts,
+                                    cudaStream_t stream) {
+  if (total < 0 || n_parts <= 0) return XRT_ERR_ARGUMENT;
+  if (total == 0) return XRT_OK;
+  xrt::launch_kernel(xrt::add_scaled_parts_kernel, dim3(xrt::grid_for((size_t)total, 256)), dim3(256), 0, stream, residual,
+                     parts, scales, (size_t)total, n_parts);
   return xrt::launch_status();
 }
 

@@ -4,5 +4,6 @@ from . import llama  # registers LlamaForCausalLM and Qwen3ForCausalLM
 from . import givopel  # registers Givopel
 from . import guzuvik  # registers Guzuvik
 from . import zogevik  # registers Zogevik
+from . import sofunex  # registers Sofunex
 
-__all__ = ["llama", "givopel", "guzuvik", "zogevik"]
+__all__ = ["llama", "givopel", "guzuvik", "zogevik", "sofunex"]

@@ -5,7 +5,7 @@ from .registry import register_part, part_class, part_kinds, ROLES
 from .context import StepContext
 from .linear import linear
 from . import (norm, rotary, embedding, attention, latent_attention, feed_forward, block, state_mixers, side_by_side,  # registers
-               stream, ssd)                                                                                      # the built-in parts
+               stream, ssd, token_shift)                                                                                      # the built-in parts
 from .block import LayerParts
 
 __all__ = ["PartSpec", "LayerSpec", "prenorm_layer", "SchedulePlace", "ModelSpec", "register_part", "part_class", "part_kinds",

@@ -11,7 +11,7 @@ import math
 
 import torch
 
-from ..cache import KVNeed
+from ..cache import KVNeed, StateNeed
 from ..core import ConfigError, DType, Unsupported, torch_dtype
 from ..csrc import ops
 from .linear import linear
@@ -54,7 +54,12 @@ class GroupedQueryAttention:
     ``q_norm`` [n_heads*head_dim] and ``k_norm`` [n_kv_heads*head_dim], before the rotation), ``sink`` (a number s: the
     softmax's denominator holds one more term exp(s) that has no value, so a head may give less than an average of
     its values), ``own_kv`` = False (the layer has no k and v products, norms or cache of its own: it is scheduled
-    with ``cache_from`` and reads the keys and values another layer cached, with its own queries, window and scale).
+    with ``cache_from`` and reads the keys and values another layer cached, with its own queries, window and scale),
+    ``conv`` (a number of taps: q, k and v pass a short causal convolution over time a channel, weights ``q_conv``,
+    ``k_conv``, ``v_conv`` [channels, taps], right after the product and its bias, before norms and rotation; the
+    last taps - 1 rows of the product are state of the sequence, so the part then asks for a ``StateNeed`` beside
+    its keys), ``v_norm`` = "unit" (every value head is divided by its root mean square, ``eps``, no weight, before it
+    is cached), ``o_bias`` (the output product has a bias ``o_bias`` [width]).
     weights: ``q`` [n_heads*head_dim, width], ``k`` [n_kv_heads*head_dim, width], ``v``
     [n_kv_heads*v_head_dim, width], ``o`` [width, n_heads*v_head_dim], with qk_norm ``q_norm``,
     ``k_norm`` [head_dim], with a gate ``g`` [n_heads*v_head_dim, width].
@@ -108,6 +113,12 @@ class GroupedQueryAttention:
                            "v_bias": ((nkv * vd,), "vector")})
         if params.get("value_blend"):
             shapes["blend"] = ((), "vector")
+        if params.get("conv"):
+            taps = int(params["conv"])
+            shapes.update({"q_conv": ((nh * hd, taps), "vector"), "k_conv": ((nkv * hd, taps), "vector"),
+                           "v_conv": ((nkv * vd, taps), "vector")})
+        if params.get("o_bias"):
+            shapes["o_bias"] = ((d,), "vector")
         return shapes
 
     def __init__(self, params, weights, dtype: DType, device):
@@ -173,10 +184,27 @@ class GroupedQueryAttention:
                                    as_row(weights["k_bias"], self.n_kv_heads, true_dim),
                                    as_row(weights["v_bias"], self.n_kv_heads, true_vdim)]).contiguous()
         self.blend = float(weights["blend"].to(torch.float32).reshape(-1)[0]) if self.value_blend else 0.0
+        # a short convolution over time on every column of the q/k/v row (taps laid out as the row is)
+        self.taps = int(params.get("conv") or 0)
+        self.conv = None
+        if self.taps:
+            if not self.own_kv or self.gate:
+                raise Unsupported("a convolution on q, k and v needs keys and values of the layer's own and no gate")
+            if not 1 <= self.taps <= 9:
+                raise ConfigError(f"a short convolution of {self.taps} taps is outside 1 to 9")
+            def taps_of(t, heads, size):
+                return _pad_rows(t.to(torch.float32), heads, size, self.head_dim)
+            self.conv = torch.cat([taps_of(weights["q_conv"], self.n_heads, true_dim),
+                                   taps_of(weights["k_conv"], self.n_kv_heads, true_dim),
+                                   taps_of(weights["v_conv"], self.n_kv_heads, true_vdim)]).contiguous()
+        self.v_unit = params.get("v_norm") == "unit"
+        if params.get("v_norm") not in (None, "unit"):
+            raise ConfigError(f"v_norm {params.get('v_norm')!r} is not unit")
+        self.o_bias = weights["o_bias"].to(torch.float32).contiguous() if params.get("o_bias") else None
         # what the rotation kernel and the kernels that fold it in do not do: these layers prepare their heads with
         # ops.qkv_heads_write and attend with the kernels that take the score options
         self.plain_heads = (self.bias is None and not self.unit_norm and not self.whole_norm and not self.value_blend
-                            and true_dim == self.head_dim)
+                            and true_dim == self.head_dim and not self.taps and not self.v_unit)
         self.plain_scores = not (self.keep_first or self.softcap or self.distance_rate) and self.sink is None
         position = params.get("position") or {"kind": "none", "params": {}}
         self.position = part_class("position", position["kind"])(position.get("params", {}), {}, dtype, device)
@@ -188,7 +216,10 @@ class GroupedQueryAttention:
         self.act_dtype = torch_dtype(dtype)
 
     def cache_need(self):
-        return KVNeed(self.n_kv_heads, self.head_dim, self.window, self.keep_first)
+        keys = KVNeed(self.n_kv_heads, self.head_dim, self.window, self.keep_first)
+        if self.taps > 1:  # the convolution's last taps - 1 inputs, one row of the q/k/v product each
+            return [keys, StateNeed((self.taps - 1, self.q_width + 2 * self.kv_width), "float32")]
+        return keys
 
     def takes_pending_norm(self, rows: int, device) -> bool:
         """Whether the first product of ``forward`` can finish a norm that the part before prepared."""
@@ -202,21 +233,39 @@ class GroupedQueryAttention:
         if then_norm is not None:
             ctx.then_norm = None
         attended = self.attended(h, ctx, store, owns_cache)
+        if self.o_bias is not None:
+            ops.add_row(residual, self.o_bias)
         if then_norm is not None:
             _, ctx.pending = linear(attended, self.w_o, accumulate_into=residual, then_norm=then_norm)
         else:
             linear(attended, self.w_o, accumulate_into=residual)
 
-    def mix(self, h, ctx, store, owns_cache=True):
-        """The mixer's result, float32 [T, width], for a caller that does something else with it than adding it."""
+    def mix(self, h, ctx, store, owns_cache=True, out=None):
+        """The mixer's result, float32 [T, width], for a caller that does something else with it than adding it
+        (written into ``out`` where that is given)."""
         ctx.then_norm = None
-        return linear(self.attended(h, ctx, store, owns_cache), self.w_o, out_dtype=torch.float32)
+        y = linear(self.attended(h, ctx, store, owns_cache), self.w_o, out_dtype=torch.float32, out=out)
+        if self.o_bias is not None:
+            ops.add_row(y, self.o_bias)
+        return y
 
     def attended(self, h, ctx, store, owns_cache=True):
         """The concatenated heads (gated if the layer has a gate) in the compute dtype, [T, heads * head size]."""
         n = h.shape[0]
         gated = self.gate is not None
+        bias = self.bias
+        if self.taps > 1:
+            if not owns_cache:
+                raise ConfigError("a layer with a convolution on q, k and v cannot read another place's state")
+            store, conv_store = store
         qkv = projected = linear(h, self.w_qkv if owns_cache or gated else self.w_q, out_dtype=torch.float32)
+        if self.taps:
+            # the product's bias is added on the convolution's way in; rows of no sequence are left alone there
+            fresh = torch.zeros if getattr(ctx, "captured", False) or sum(ctx.new_lens) < ctx.n_tokens else torch.empty
+            qkv = fresh(projected.shape, dtype=torch.float32, device=h.device)
+            ops.short_conv(qkv, projected, self.conv, conv_store.state if self.taps > 1 else None, ctx.cu_seqlens,
+                           ctx.seq_slot, ctx.max_new, "none", in_bias=bias)
+            bias = None
         window = int(self.window) if self.window else 0
         pairing = getattr(self.position, "pairing", "split_half")
         cos_sin = self.position.tables(ctx)
@@ -245,14 +294,14 @@ class GroupedQueryAttention:
                     if v_first is None:  # the first layer of this name in the step: its values are the ones blended in
                         v_keep = torch.zeros((n, self.n_kv_heads * self.true_vdim), dtype=torch.float32, device=h.device)
                         ctx.shared[("value_blend", self.value_blend)] = v_keep
-                ops.qkv_heads_write(q, store.k, store.v, qkv, self.q_width, self.q_width + self.kv_width, self.bias,
+                ops.qkv_heads_write(q, store.k, store.v, qkv, self.q_width, self.q_width + self.kv_width, bias,
                                     self.unit_norm, self.true_dim, self.eps, ctx.tok_slot, ctx.tok_pos, store.block_table,
                                     self.n_heads, self.n_kv_heads, self.head_dim, v_keep=v_keep, v_first=v_first,
                                     v_blend=self.blend if v_first is not None else 0.0, v_dim=self.true_vdim,
                                     write_kv=owns_cache, q_norm_w=self.q_norm, k_norm_w=self.k_norm if owns_cache else None,
                                     whole_q=self.n_heads * self.true_dim if self.whole_norm else 0,
                                     whole_k=self.n_kv_heads * self.true_dim if self.whole_norm else 0,
-                                    cos_sin=cos_sin, pairing=pairing)
+                                    cos_sin=cos_sin, pairing=pairing, v_unit=self.v_unit)
             self.attend(attended, q, ctx, store)
         if self.gate == "sigmoid_head":
             ops.gate_mul(attended, projected[:, self.gate_offset:], "sigmoid", group=self.head_dim)

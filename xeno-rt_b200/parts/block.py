@@ -79,10 +79,17 @@ def sandwich_residual(parts: LayerParts, x, ctx, stores, owns_cache: bool) -> No
     ``ffn``, ``ffn_post``.  The mixer hands its result back (``mix``), the feed-forward too (``apply``: [T, width] or
     [parts, T, width] float32), and the norm after it adds into the 32-bit stream (``add_into``).
     The norm after a sublayer also computes the norm that the next sublayer begins with, in the same pass over the
-    row (its own feed-forward's, or the first norm of the layer that runs next, left in ``ctx.pending``)."""
+    row (its own feed-forward's, or the first norm of the layer that runs next, left in ``ctx.pending``).
+    A layer may have a part ``mixer_shift`` (role ``shift``): the mixer then reads its norm blended with that of the
+    token before; such a layer's first norm is never prepared by the layer before it."""
     ready = ctx.take_pending(parts.mixer_norm)
-    h = ready.value if ready is not None else parts.mixer_norm.forward(x)
     after = ctx.shared.get("next_layer")  # (first norm, the part that takes it) of the layer that runs next, or None
+    if after is not None and len(after) > 2 and "mixer_shift" in after[2]:
+        after = None  # that layer's first norm is blended with the token before: it runs it itself
+    if "mixer_shift" in parts:
+        h = parts.mixer_shift.forward(x, parts.mixer_norm, ctx, stores.get("mixer_shift"), owns_cache)
+    else:
+        h = ready.value if ready is not None else parts.mixer_norm.forward(x)
     has_ffn = "ffn" in parts
     following = parts.ffn_norm if has_ffn else (after[0] if after else None)
     h = parts.mixer_post.add_into(x, parts.mixer.mix(h, ctx, stores.get("mixer"), owns_cache), then=following)
@@ -142,7 +149,7 @@ class ReadyNorm:
         self.norm, self.value = norm, value
 
 
-sandwich_residual.first_norm = lambda parts: (parts.mixer_norm, parts.mixer)
+sandwich_residual.first_norm = lambda parts: (parts.mixer_norm, parts.mixer, parts)
 register_part("arrangement", "parallel_residual", parallel_residual)
 register_part("arrangement", "sandwich_residual", sandwich_residual)
 

@@ -9,8 +9,8 @@ from .registry import register_part
 
 
 class TokenEmbedding:
-    """x = E[token], no scaling (crates/xrt-models/src/llama.rs:1042-1055).
-    params: ``vocab_size``, ``width``.  weights: ``weight`` [vocab, width]."""
+    """x = E[token], no scaling (crates/xrt-models/src/llama.rs:1042-1055); with ``scale`` x = E[token] * scale (32-bit).
+    params: ``vocab_size``, ``width``, optional ``scale``.  weights: ``weight`` [vocab, width]."""
 
     graph_safe = True
 
@@ -22,10 +22,11 @@ class TokenEmbedding:
         self.vocab_size = int(params["vocab_size"])
         self.width = int(params["width"])
         self.weight = weights["weight"]
+        self.scale = float(params.get("scale") or 1.0)
 
     def forward(self, token_ids, error_flag):
         out = torch.empty((token_ids.numel(), self.width), dtype=torch.float32, device=token_ids.device)
-        ops.embedding(out, self.weight, token_ids, error_flag)
+        ops.embedding(out, self.weight, token_ids, error_flag, self.scale)
         return out
 
 

@@ -12,7 +12,8 @@ from .registry import register_part
 
 
 class SwiGLUFeedForward:
-    """params: ``width``, ``inner`` (the feed-forward width).
+    """params: ``width``, ``inner`` (the feed-forward width); optional ``activation`` of the gate: "silu" (default) or
+    "gelu_tanh" (the tanh form of gelu: down( gelu_tanh(gate(h)) * up(h) )).
     weights: ``gate``, ``up`` [inner, width], ``down`` [width, inner]."""
 
     graph_safe = True
@@ -36,23 +37,35 @@ class SwiGLUFeedForward:
             self.w_gate_up = torch.cat([weights["gate"], weights["up"]], dim=0).contiguous()
         self.w_down = weights["down"]
         self.act_dtype = torch_dtype(dtype)
+        self.activation = params.get("activation", "silu")
+        if self.activation not in ops.GATE_ACTS:
+            raise ConfigError(f"the gate's activation {self.activation!r} is not one of {sorted(ops.GATE_ACTS)}")
 
     def takes_pending_norm(self, rows: int, device) -> bool:
         """Whether the first product of ``forward`` can finish a norm that the part before prepared."""
-        if self.act_dtype != torch.bfloat16:
+        if self.act_dtype != torch.bfloat16 or self.activation != "silu":
             return False
         from . import linear_bf16
         return linear_bf16.takes_pending(rows, self.inner, self.width, "swiglu", device)
 
-    def forward(self, h, residual, ctx):
+    def _act(self, h):
         act = torch.empty((h.shape[0], self.inner), dtype=self.act_dtype, device=h.device)
         fused = False
-        if self.act_dtype == torch.bfloat16 and h.dtype == torch.bfloat16:
+        if self.act_dtype == torch.bfloat16 and h.dtype == torch.bfloat16 and self.activation == "silu":
             from . import linear_bf16
             fused = linear_bf16.run_swiglu(act, h, self.w_gate_up, self.inner)
         if not fused:
             gate_up = linear(h, self.w_gate_up, out_dtype=torch.float32)
-            ops.swiglu(act, gate_up)
+            ops.swiglu(act, gate_up, self.activation)
+        return act
+
+    def apply(self, h, ctx, out=None):
+        """The result handed back, float32 [T, width] (written into ``out`` where that is given)."""
+        ctx.then_norm = None
+        return linear(self._act(h), self.w_down, out_dtype=torch.float32, out=out)
+
+    def forward(self, h, residual, ctx):
+        act = self._act(h)
         # the last product may prepare the norm that follows this part (ctx.then_norm, see parts/context.py)
         if getattr(ctx, "then_norm", None) is not None:
             _, ctx.pending = linear(act, self.w_down, accumulate_into=residual, then_norm=ctx.then_norm)
@@ -104,7 +117,15 @@ class RoutedExperts:
     ``routing`` = "scores": the weights are the softmax of the logits over ALL experts, as they are (not renormalized
     over the chosen); with ``groups`` (a number of equal groups of neighbouring experts) and ``keep_groups``, only
     experts of the ``keep_groups`` groups whose best score is largest can be chosen.  ``router_bias`` = False: the
-    router has no bias tensor."""
+    router has no bias tensor.
+    ``activation`` = "gated_silu": an expert is W_down (silu(W_gate h) * (W_up h)), no limits.
+    More options of ``routing`` = "scores": ``scores`` = "sigmoid" (every score is the sigmoid of its logit, not the
+    softmax over all); ``correction`` = True (a tensor ``correction`` [experts] is added to the scores for every choice,
+    of groups and of experts, but not for the weights); ``group_best`` (a group counts by the sum of so many of its
+    largest choice scores, default 1); ``normalize`` (the chosen weights are divided by their sum + ``sum_eps``);
+    ``weight_scale`` (they are multiplied by it).
+    ``shared`` (an inner width): one more gated silu feed-forward ``shared_gate``, ``shared_up`` [shared, width],
+    ``shared_down`` [width, shared] that every token uses with weight 1; its result is one more part of ``apply``'s."""
 
     graph_safe = True
 
@@ -112,12 +133,22 @@ class RoutedExperts:
     def _gated(params) -> bool:
         return params.get("activation", "gated_sigmoid") != "gelu"
 
+    @staticmethod
+    def _shared_spec(params):
+        """(role prefix, params) of the shared feed-forward, or None."""
+        if not params.get("shared"):
+            return None
+        return {"width": params["width"], "inner": int(params["shared"]), "activation": "silu"}
+
     @classmethod
     def fused_weights(cls, params):
         n = int(params["experts"])
         first = (lambda i: (f"gate{i}", f"up{i}")) if cls._gated(params) else (lambda i: (f"up{i}",))
-        return {"experts_in": tuple(r for i in range(n) for r in first(i)),
-                "experts_out": tuple(f"down{i}" for i in range(n))}
+        fused = {"experts_in": tuple(r for i in range(n) for r in first(i)),
+                 "experts_out": tuple(f"down{i}" for i in range(n))}
+        if cls._shared_spec(params):
+            fused["shared_gate_up"] = ("shared_gate", "shared_up")
+        return fused
 
     @classmethod
     def weight_shapes(cls, params):
@@ -129,12 +160,30 @@ class RoutedExperts:
             shapes.update({f"up{i}": ((f, d), "matrix"), f"down{i}": ((d, f), "matrix")})
             if cls._gated(params):
                 shapes[f"gate{i}"] = ((f, d), "matrix")
+        if params.get("correction"):
+            shapes["correction"] = ((n,), "vector")
+        shared = cls._shared_spec(params)
+        if shared:
+            for role, shape in SwiGLUFeedForward.weight_shapes(shared).items():
+                shapes["shared_" + role] = shape
         return shapes
 
     def __init__(self, params, weights, dtype: DType, device):
         self.width, self.inner = int(params["width"]), int(params["inner"])
         self.experts, self.top = int(params["experts"]), int(params["top"])
-        self.act = "gated_sigmoid" if self._gated(params) else "gelu"
+        self.act = params.get("activation", "gated_sigmoid")
+        if self.act not in ops.MOE_ACTS:
+            raise ConfigError(f"experts' activation {self.act!r} is not one of {sorted(ops.MOE_ACTS)}")
+        self.scores = params.get("scores", "softmax")
+        self.group_best = int(params.get("group_best") or 1)
+        self.normalize, self.sum_eps = bool(params.get("normalize")), float(params.get("sum_eps") or 0.0)
+        self.weight_scale = float(params.get("weight_scale") or 1.0)
+        self.correction = weights["correction"].to(torch.float32).contiguous() if params.get("correction") else None
+        self.shared = None
+        shared = self._shared_spec(params)
+        if shared:
+            own = {role[len("shared_"):]: t for role, t in weights.items() if role.startswith("shared_")}
+            self.shared = SwiGLUFeedForward(shared, own, dtype, device)
         self.limit, self.alpha = float(params.get("limit") or 0.0), float(params.get("alpha") or 0.0)
         self.routing = params.get("routing", "top_softmax")
         if self.routing not in ("top_softmax", "scores"):
@@ -167,7 +216,9 @@ class RoutedExperts:
         if self.routing == "scores":
             if self.router_bias is not None:
                 logits += self.router_bias
-            ops.moe_route_scores(ids, weights, logits, self.top, self.groups, self.keep_groups)
+            ops.moe_route_scores(ids, weights, logits, self.top, self.groups, self.keep_groups, scores=self.scores,
+                                 correction=self.correction, group_best=self.group_best, normalize=self.normalize,
+                                 sum_eps=self.sum_eps, scale=self.weight_scale)
         else:
             ops.moe_route(ids, weights, logits, self.router_bias, self.top)
         return ids, weights
@@ -183,13 +234,16 @@ class RoutedExperts:
         once (prompts only)."""
         n = h.shape[0]
         ids, weights = self.route(h)
-        out = torch.empty((self.top, n, self.width), dtype=torch.float32, device=h.device)
+        whole = torch.empty((self.top + (1 if self.shared else 0), n, self.width), dtype=torch.float32, device=h.device)
+        out = whole[:self.top]
+        if self.shared:
+            self.shared.apply(h, ctx, out=whole[self.top])
         pairs = n * self.top
         one_launch = h.dtype == torch.bfloat16 and self.width % 8 == 0 and self.inner % 8 == 0
         fixed_shapes = getattr(ctx, "captured", False) or ctx.all_single  # no read-back inside such a step
         if pairs < self.GROUPED_FROM * self.experts or (fixed_shapes and not one_launch):
             ops.moe_experts(out, h, self.w_in, self.w_out, ids, weights, self.inner, self.limit, self.alpha, act=self.act)
-            return out
+            return whole
         offsets = torch.empty((self.experts + 1,), dtype=torch.int32, device=h.device)
         pos = torch.empty((pairs,), dtype=torch.int32, device=h.device)
         row_token = torch.empty((pairs,), dtype=torch.int32, device=h.device)
@@ -210,17 +264,17 @@ class RoutedExperts:
             for e in range(self.experts):
                 lo, hi = bounds[e], bounds[e + 1]
                 if hi > lo:
-                    first = (2 if self.act == "gated_sigmoid" else 1) * self.inner  # rows of an expert in the first buffer
+                    first = (1 if self.act == "gelu" else 2) * self.inner  # rows of an expert in the first buffer
                     gate_up = linear(rows[lo:hi], self.w_in[e * first:(e + 1) * first], out_dtype=torch.float32)
                     ops.moe_activation(act[lo:hi], gate_up, self.limit, self.alpha, kind=self.act)
                     linear(act[lo:hi], self.w_out[e * self.width:(e + 1) * self.width], accumulate_into=y[lo:hi])
         ops.moe_combine(out, y, pos, weights)
-        return out
+        return whole
 
     def forward(self, h, residual, ctx):
         ctx.then_norm = None
         parts = self.apply(h, ctx)
-        for c in range(self.top):
+        for c in range(parts.shape[0]):
             residual.add_(parts[c])
 
 

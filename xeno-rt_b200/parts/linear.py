@@ -8,16 +8,22 @@ from ..core import KernelError
 from ..csrc import ops
 
 
-def linear(x, weight: torch.Tensor, out_dtype=None, accumulate_into: torch.Tensor | None = None, then_norm=None):
+def linear(x, weight: torch.Tensor, out_dtype=None, accumulate_into: torch.Tensor | None = None, then_norm=None,
+           out: torch.Tensor | None = None):
     """Returns x . weight^T in ``out_dtype`` (default float32), or, with ``accumulate_into`` (a
     float32 tensor [M, N], the residual stream), adds the product into it in place and returns it.
     Accumulation is 32-bit in every kernel.  ``x`` may be a ``PendingNorm`` (see parts/norm.py).
     ``then_norm`` (an RMSNorm part, with ``accumulate_into``): if the kernel that runs can prepare that
-    norm of the new residual on its way, the result is (residual, PendingNorm), else (residual, None)."""
+    norm of the new residual on its way, the result is (residual, PendingNorm), else (residual, None).
+    ``out`` (a contiguous tensor [M, N]): the product is written there instead of into a new tensor."""
+    if out is not None and (accumulate_into is not None or tuple(out.shape) != (x.shape[0], weight.shape[0])
+                            or not out.is_contiguous()):
+        raise KernelError("linear: out must be a contiguous [rows, weight rows] tensor, and not given with accumulate_into")
     from .norm import PendingNorm
     if isinstance(x, PendingNorm):
         from . import linear_bf16
-        out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype or torch.float32, device=x.device)
+        if out is None:
+            out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype or torch.float32, device=x.device)
         linear_bf16.run_pending(out, x, weight)
         return out
     m = x.shape[0]
@@ -26,7 +32,7 @@ def linear(x, weight: torch.Tensor, out_dtype=None, accumulate_into: torch.Tenso
         out = accumulate_into
         if out.dtype != torch.float32:
             raise KernelError("linear: the residual stream must be float32")
-    else:
+    elif out is None:
         out = torch.empty((m, n), dtype=out_dtype or torch.float32, device=x.device)
     accumulate = accumulate_into is not None
     pending = None

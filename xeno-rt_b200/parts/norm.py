@@ -38,8 +38,19 @@ class PendingNorm:
         return self.scaled.device
 
 
+@dataclass
+class WeightedParts:
+    """A sublayer's result that is still in parts: ``parts`` float32 [n, T, width], their sum sum_p scales[p] *
+    parts[p] + bias being the result (``scales`` float32 [n] on the device, ``bias`` float32 [width] or None).  The
+    norm that follows the sublayer adds them up in its own pass over the row."""
+    parts: torch.Tensor
+    scales: torch.Tensor
+    bias: torch.Tensor | None = None
+
+
 class RMSNorm:
-    """params: ``width``, ``eps``.  weights: ``weight`` [width]."""
+    """params: ``width``, ``eps``; optional ``gain`` (a number g: ``add_into`` adds g times the norm; ``forward`` does
+    not use it).  weights: ``weight`` [width]."""
 
     graph_safe = True
 
@@ -51,6 +62,7 @@ class RMSNorm:
         self.width = int(params["width"])
         self.eps = float(params["eps"])
         self.weight = weights["weight"]
+        self.gain = float(params.get("gain") or 1.0)
         self.out_dtype = torch_dtype(dtype)
 
     def forward(self, x, rows=None):
@@ -65,16 +77,25 @@ class RMSNorm:
         ops.rmsnorm(out, x, self.weight, self.eps, None)
         return out
 
-    def add_into(self, residual, y, copy: bool = False):
-        """residual += norm(y), 32-bit (a norm that follows a sublayer).  ``y`` float32 [T, width] or [parts, T,
-        width], whose parts are added in index order first.  ``copy``: the new residual is also returned in the
-        compute dtype, written in the same pass (what the next sublayer's products read), else None."""
-        if y.dim() == 3 and y.shape[0] == 1:
+    def add_into(self, residual, y, copy: bool = False, then=None):
+        """residual += gain * norm(y), 32-bit (a norm that follows a sublayer).  ``y`` float32 [T, width] or [parts, T,
+        width], whose parts are added in index order first; or a ``WeightedParts`` (parts with a factor each and a
+        row added to their sum).  ``copy``: the new residual is also returned in the compute dtype, written in the
+        same pass (what the next sublayer's products read), else None.  ``then``: another RMSNorm of this width whose
+        weight has this one's dtype; its result over the new residual is returned, computed in the same pass (else None)."""
+        scales = bias = None
+        if isinstance(y, WeightedParts):
+            y, scales, bias = y.parts, y.scales, y.bias
+        if y.dim() == 3 and y.shape[0] == 1 and scales is None:
             y = y[0]
-        out = None
+        out = following = None
         if copy:
             out = torch.empty(residual.shape, dtype=self.out_dtype, device=residual.device)
-        ops.rmsnorm_add(residual, y, self.weight, self.eps, copy=out)
+        elif isinstance(then, RMSNorm) and then.width == self.width and then.weight.dtype == self.weight.dtype:
+            out = torch.empty(residual.shape, dtype=then.out_dtype, device=residual.device)
+            following = (then.weight, then.eps, out)
+        ops.rmsnorm_add(residual, y, self.weight, self.eps, copy=out if copy else None, factor=self.gain,
+                        part_scales=scales, bias=bias, then=following)
         return out
 
 

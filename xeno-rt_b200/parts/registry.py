@@ -19,6 +19,8 @@ embedding       ``forward(token_ids, error_flag) -> x`` float32 [T, D].
 lm_head         ``forward(normed) -> logits`` float32 [R, V].
 stream          ``forward(x, x0, ctx) -> x``: a step on the residual stream between layers; ``x0`` is what
                 the embedding gave.  It may return a new tensor.  A ``SchedulePlace`` names it in ``before``.
+shift           ``cache_need() -> StateNeed`` and ``forward(x, norm, ctx, store, owns_cache) -> h``: the norm of the
+                stream blended with what it was for the token before (kept for every sequence).
 A mixer may also have ``mix(h, ctx, store, owns_cache) -> float32 [T, D]``: its result handed back instead
 of added, for a mixer that is made of other mixers.
 A part class may set ``graph_safe = True`` to say that its ``forward`` only launches device work
@@ -36,7 +38,7 @@ from __future__ import annotations
 
 from ..core import ConfigError
 
-ROLES = ("norm", "mixer", "feed_forward", "position", "embedding", "lm_head", "arrangement", "stream")
+ROLES = ("norm", "mixer", "feed_forward", "position", "embedding", "lm_head", "arrangement", "stream", "shift")
 _REGISTRY: dict[str, dict[str, object]] = {role: {} for role in ROLES}
 
 

@@ -61,7 +61,8 @@ class BlendedRotaryEncoding:
     hi = min(ceil(d(slow)), rope_dim - 1); cos and sin are multiplied by 0.1 ln(factor) + 1.
     params: ``rope_dim``, ``base``, ``pairing``, and ``scaling`` = None or a dict with ``factor``,
     ``original`` (positions the frequencies were made for), ``fast`` and ``slow`` (turns over those
-    positions).  No weights.  The frequencies are worked out once in float64 and kept as two 32-bit
+    positions); ``divide`` (optional, a number: every frequency is divided by it, the scaling known as linear or
+    position interpolation; with ``scaling`` it applies first).  No weights.  The frequencies are worked out once in float64 and kept as two 32-bit
     terms; a step's angles are 32-bit products of position and frequency whose rounding error is carried along, so
     that far positions turn as exactly as near ones."""
 
@@ -83,6 +84,10 @@ class BlendedRotaryEncoding:
         self.half = self.rope_dim // 2
         i = np.arange(self.half, dtype=np.float64)
         freq = np.power(self.base, -2.0 * i / self.rope_dim)
+        divide = float(params.get("divide") or 1.0)
+        if not divide > 0:
+            raise ConfigError(f"rotary divide {divide} must be positive")
+        freq = freq / divide
         self.magnitude = 1.0
         scaling = params.get("scaling")
         if scaling:
@@ -98,7 +103,7 @@ class BlendedRotaryEncoding:
         self.freq = torch.from_numpy(freq.astype(np.float32)).to(device)
         # what the 32-bit frequency lost: the table kernel carries it, and its product's rounding error, into the angle
         self.freq_lo = torch.from_numpy((freq - freq.astype(np.float32).astype(np.float64)).astype(np.float32)).to(device)
-        self._key = ("blended_rotary", self.rope_dim, self.base, repr(sorted((scaling or {}).items())))
+        self._key = ("blended_rotary", self.rope_dim, self.base, divide, repr(sorted((scaling or {}).items())))
 
     def tables(self, ctx):
         """magnitude * (cos, sin) float32 [T, half, 2] for the tokens of the step; computed once a step."""

@@ -4,6 +4,10 @@ over the model width with a weight of its own, and the mean of those is the mixe
 params: ``width``, ``eps``, ``branches``: a list of ``{"name", "kind", "params"}`` naming registered mixers
 (each must offer ``mix``).  weights: for branch ``name`` the branch's own tensors under ``<name>.<role>``
 and its norm weight under ``<name>.out`` [width].  The cache need is the list of the branches' needs.
+
+``combine`` = "weighted" instead: the result is sum_b scale_b * result_b with a number ``scale`` in every branch's
+dict; no norms and no ``<name>.out`` weights.  Such a mixer hands its result back in parts (``mix`` returns a
+``WeightedParts``: the norm that follows it adds them up), or adds them into the stream itself (``forward``).
 """
 from __future__ import annotations
 
@@ -36,11 +40,15 @@ class SideBySideMixer:
         for name, branch_cls, branch_params in cls._branches(params):
             for role, shape in branch_cls.weight_shapes(branch_params).items():
                 shapes[f"{name}.{role}"] = shape
-            shapes[f"{name}.out"] = ((params["width"],), "vector")
+            if params.get("combine", "normed_mean") != "weighted":
+                shapes[f"{name}.out"] = ((params["width"],), "vector")
         return shapes
 
     def __init__(self, params, weights, dtype, device):
-        self.width, self.eps = int(params["width"]), float(params["eps"])
+        self.width, self.eps = int(params["width"]), float(params.get("eps") or 0.0)
+        self.combine = params.get("combine", "normed_mean")
+        if self.combine not in ("normed_mean", "weighted"):
+            raise ConfigError(f"side-by-side mixers are combined as normed_mean or weighted, not {self.combine!r}")
         self.branches, self.out_weights = [], []
         for name, branch_cls, branch_params in self._branches(params):
             if not hasattr(branch_cls, "mix"):
@@ -48,7 +56,10 @@ class SideBySideMixer:
             own = {role[len(name) + 1:]: t for role, t in weights.items()
                    if role.startswith(name + ".") and role != f"{name}.out"}
             self.branches.append(branch_cls(branch_params, own, dtype, device))
-            self.out_weights.append(weights[f"{name}.out"].to(torch.float32).contiguous())
+            if self.combine != "weighted":
+                self.out_weights.append(weights[f"{name}.out"].to(torch.float32).contiguous())
+        if self.combine == "weighted":
+            self.scales = torch.tensor([float(b["scale"]) for b in params["branches"]], dtype=torch.float32, device=device)
         if not self.branches:
             raise ConfigError("a side-by-side mixer needs at least one branch")
         self.graph_safe = all(getattr(b, "graph_safe", False) for b in self.branches)
@@ -56,8 +67,23 @@ class SideBySideMixer:
     def cache_need(self):
         return [b.cache_need() for b in self.branches]
 
+    def mix(self, h, ctx, store, owns_cache=True):
+        """The branches' results as parts with their factors (``combine`` "weighted" only)."""
+        from .norm import WeightedParts
+        if self.combine != "weighted":
+            raise ConfigError("side-by-side mixers whose results are normed and averaged add into the stream themselves")
+        ctx.then_norm = None
+        parts = torch.empty((len(self.branches), h.shape[0], self.width), dtype=torch.float32, device=h.device)
+        for i, (branch, branch_store) in enumerate(zip(self.branches, store)):
+            branch.mix(h, ctx, branch_store, owns_cache, out=parts[i])
+        return WeightedParts(parts, self.scales)
+
     def forward(self, h, residual, ctx, store, owns_cache=True):
         ctx.then_norm = None
+        if self.combine == "weighted":
+            y = self.mix(h, ctx, store, owns_cache)
+            ops.add_scaled_parts(residual, y.parts, y.scales)
+            return
         share = 1.0 / len(self.branches)
         for branch, weight, branch_store in zip(self.branches, self.out_weights, store):
             y = branch.mix(h, ctx, branch_store, owns_cache)

@@ -1,5 +1,6 @@
-"""Mixers that keep a matrix state per head instead of keys and values: gated linear attention and the
-gated delta rule.  Both run the same scan kernel (csrc/state_mixers.cu) over the tokens of a step,
+"""Mixers that keep a matrix state per head instead of keys and values: gated linear attention, the gated delta
+rule, and a delta rule with a decay and a removal rate per key channel (``DecayRemovalRule``, whose recurrence is in
+its own text).  All run the same scan kernel (csrc/state_mixers.cu) over the tokens of a step,
 
     S_t = diag(a_t) S_(t-1) + k_t u_t^T,        o_t = S_t^T q_t,
 
@@ -34,9 +35,9 @@ class _StateMixer:
         ctx.then_norm = None
         linear(self.heads_out(h, ctx, store, owns_cache), self.w_o, accumulate_into=residual)
 
-    def mix(self, h, ctx, store, owns_cache=True):
+    def mix(self, h, ctx, store, owns_cache=True, out=None):
         ctx.then_norm = None
-        return linear(self.heads_out(h, ctx, store, owns_cache), self.w_o, out_dtype=torch.float32)
+        return linear(self.heads_out(h, ctx, store, owns_cache), self.w_o, out_dtype=torch.float32, out=out)
 
     @staticmethod
     def _rows(ctx):
@@ -177,5 +178,63 @@ class GatedDeltaRule(_StateMixer):
         return y
 
 
+class DecayRemovalRule(_StateMixer):
+    """r = W_r h, k = W_k h, v = W_v h, all heads of ``dim``.  Per head and key channel a decay
+    w = exp(-decay_rate * sigmoid(W_w2 tanh(W_w1 h) + w0)) and a removal rate a = sigmoid(W_a h + a_bias).  With the
+    unit key n = k / sqrt(sum(k^2) + unit_eps) of a head, its state S [key, value] becomes
+    S <- diag(w) S - (a * n) (n^T S) + k v^T, the decay and the removal both reading the state as the token found it,
+    and o = S^T r.  Every head's o is divided by its root mean square (``eps``), times the weight ``norm`` (one a column
+    of all heads), times sigmoid(W_g h); then W_o.  State, decays, rates, unit keys and head norms are 32-bit.
+    params: ``width``, ``n_heads``, ``dim``, ``decay_rank`` (rows of w1), ``eps``, ``decay_rate``, ``unit_eps``.
+    weights: ``r``, ``k``, ``v``, ``g``, ``a`` [heads * dim, width], ``a_bias``, ``w0``, ``norm`` [heads * dim],
+    ``w1`` [decay_rank, width], ``w2`` [heads * dim, decay_rank], ``o`` [width, heads * dim]."""
+
+    @classmethod
+    def fused_weights(cls, params):
+        return {"rkvgaw": ("r", "k", "v", "g", "a", "w1")}
+
+    @classmethod
+    def weight_shapes(cls, params):
+        d, nh, hd, rank = (params[k] for k in ("width", "n_heads", "dim", "decay_rank"))
+        shapes = {r: ((nh * hd, d), "matrix") for r in ("r", "k", "v", "g", "a")}
+        shapes.update({"w1": ((rank, d), "matrix"), "w2": ((nh * hd, rank), "matrix"), "o": ((d, nh * hd), "matrix"),
+                       "a_bias": ((nh * hd,), "vector"), "w0": ((nh * hd,), "vector"), "norm": ((nh * hd,), "vector")})
+        return shapes
+
+    def __init__(self, params, weights, dtype: DType, device):
+        self.n_heads, self.dim, self.decay_rank = (int(params[k]) for k in ("n_heads", "dim", "decay_rank"))
+        self.eps, self.decay_rate, self.unit_eps = (float(params[k]) for k in ("eps", "decay_rate", "unit_eps"))
+        if not self.decay_rate > 0:
+            raise ConfigError(f"decay_rate {self.decay_rate} must be positive")
+        self.w_in = weights.get("rkvgaw")
+        if self.w_in is None:
+            self.w_in = torch.cat([weights[r] for r in ("r", "k", "v", "g", "a", "w1")], dim=0).contiguous()
+        self.w_w2, self.w_o = weights["w2"], weights["o"]
+        self.a_bias, self.w0, self.norm = _vector(weights["a_bias"]), _vector(weights["w0"]), _vector(weights["norm"])
+        self.act_dtype = torch_dtype(dtype)
+
+    def cache_need(self):
+        return StateNeed((self.n_heads, self.dim, self.dim), "float32")
+
+    def heads_out(self, h, ctx, store, owns_cache=True):
+        self._owning(owns_cache)
+        nh, hd = self.n_heads, self.dim
+        n, w = h.shape[0], self.n_heads * self.dim
+        p = linear(h, self.w_in, out_dtype=torch.float32)                   # r | k | v | g | a | w1 h
+        low = torch.empty((n, self.decay_rank), dtype=self.act_dtype, device=h.device)
+        ops.act_cast(low, p[:, 5 * w:], "tanh")
+        decay = linear(low, self.w_w2, out_dtype=torch.float32)
+        unit = torch.empty((n, w), dtype=torch.float32, device=h.device)
+        removal = p[:, 4 * w:5 * w]
+        ops.removal_gates(decay, self.w0, removal, self.a_bias, unit, p[:, w:2 * w], nh, hd, self.decay_rate, self.unit_eps)
+        o = self._rows(ctx)((n, w), dtype=torch.float32, device=h.device)
+        ops.state_scan(o, p, p[:, w:], p[:, 2 * w:], decay, None, store.state, ctx.cu_seqlens, ctx.seq_slot, nh, nh, hd, hd,
+                       max_new=ctx.max_new, unit=unit, removal=removal)
+        y = torch.empty((n, w), dtype=self.act_dtype, device=h.device)
+        ops.head_norm_gate(y, o, self.norm, p[:, 3 * w:], nh, hd, self.eps, "sigmoid")
+        return y
+
+
+register_part("mixer", "decay_removal_rule", DecayRemovalRule)
 register_part("mixer", "gated_linear_attention", GatedLinearAttention)
 register_part("mixer", "gated_delta_rule", GatedDeltaRule)

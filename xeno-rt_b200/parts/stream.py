@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from ..core import torch_dtype
+from ..core import ConfigError, torch_dtype
 from ..csrc import ops
 from .linear import linear
 from .registry import register_part
@@ -52,5 +52,28 @@ class NormedStream:
         return out
 
 
+class AddRow:
+    """x <- x + R[row] in 32-bit, in place: one row of a table is added to every token's stream (a model that runs a
+    stretch of layers several times may begin each pass with a row of its own).
+    params: ``width``, ``rows`` (of the table), ``row``.  weights: ``weight`` [rows, width]."""
+
+    graph_safe = True
+
+    @classmethod
+    def weight_shapes(cls, params):
+        return {"weight": ((params["rows"], params["width"]), "matrix")}
+
+    def __init__(self, params, weights, dtype, device):
+        row, rows = int(params["row"]), int(params["rows"])
+        if not 0 <= row < rows:
+            raise ConfigError(f"row {row} is outside the table's {rows} rows")
+        self.row = weights["weight"][row].to(torch.float32).contiguous()
+
+    def forward(self, x, x0, ctx):
+        ops.add_row(x, self.row)
+        return x
+
+
+register_part("stream", "add_row", AddRow)
 register_part("stream", "mix_with_embedding", MixWithEmbedding)
 register_part("stream", "rmsnorm", NormedStream)
