@@ -148,8 +148,8 @@ def delta_side(h, w, prefix, m, eps):
 
 
 def mixer(h, w, prefix, m, eps):
-    return (m["left_scale"] * attention_side(h, w, prefix + "left.", m["left"], eps)
-            + m["right_scale"] * delta_side(h, w, prefix + "right.", m["right"], eps))
+    return (m.get("left_scale", 1.0) * attention_side(h, w, prefix + "left.", m["left"], eps)
+            + m.get("right_scale", 1.0) * delta_side(h, w, prefix + "right.", m["right"], eps))
 
 
 # ----------------------------------------------------------------------------- feed-forwards
@@ -159,26 +159,35 @@ def gated(h, w, prefix, act):
 
 
 def route(h_row, w, prefix, mlp):
-    """(experts, weights) of one token."""
+    """(experts, weights, margin) of one token; the margin is the smallest lead, in choice scores, by which a kept
+    group or a chosen expert won its place (infinite where nothing was left out)."""
     router = mlp["router"]
     n, top = router["experts"], router["top"]
     scores = sigmoid(w[prefix + "router"].astype(F64) @ h_row)
     choice = scores + w[prefix + "correction"].astype(F64)
+    margin = np.inf
     groups = router.get("groups")
     if groups and groups["keep"] < groups["count"]:
         size = n // groups["count"]
         worth = [np.sort(choice[g * size:(g + 1) * size])[-GROUP_BEST:].sum() for g in range(groups["count"])]
-        kept = sorted(range(groups["count"]), key=lambda g: (-worth[g], g))[:groups["keep"]]
+        ranked = sorted(range(groups["count"]), key=lambda g: (-worth[g], g))
+        kept = ranked[:groups["keep"]]
+        margin = worth[ranked[groups["keep"] - 1]] - worth[ranked[groups["keep"]]]
         choice = np.array([c if e // size in kept else -np.inf for e, c in enumerate(choice)])
-    chosen = sorted(range(n), key=lambda e: (-choice[e], e))[:top]
+    ranked = sorted(range(n), key=lambda e: (-choice[e], e))
+    chosen = ranked[:top]
+    if top < n and np.isfinite(choice[ranked[top]]):
+        margin = min(margin, choice[ranked[top - 1]] - choice[ranked[top]])
     weights = scores[chosen] / (scores[chosen].sum() + WEIGHT_SUM_EPS) * router["scale"]
-    return chosen, weights
+    return chosen, weights, margin
 
 
-def experts(h, w, prefix, mlp):
+def experts(h, w, prefix, mlp, margins=None):
     out = np.zeros((h.shape[0], w[prefix + "e0.down"].shape[0]))
     for t in range(h.shape[0]):
-        chosen, weights = route(h[t], w, prefix, mlp)
+        chosen, weights, margin = route(h[t], w, prefix, mlp)
+        if margins is not None:
+            margins[t] = min(margins[t], margin)
         for e, weight in zip(chosen, weights):
             out[t] += weight * gated(h[t:t + 1], w, f"{prefix}e{e}.", silu)[0]
     if mlp.get("shared"):
@@ -186,8 +195,8 @@ def experts(h, w, prefix, mlp):
     return out
 
 
-def feed_forward(h, w, prefix, mlp):
-    return gated(h, w, prefix, gelu_tanh) if mlp["kind"] == "dense" else experts(h, w, prefix, mlp)
+def feed_forward(h, w, prefix, mlp, margins=None):
+    return gated(h, w, prefix, gelu_tanh) if mlp["kind"] == "dense" else experts(h, w, prefix, mlp, margins)
 
 
 # ----------------------------------------------------------------------------- the model
@@ -202,24 +211,25 @@ def layer_order(config):
     return order + [(i, None) for i in range(loop["stop"], n)]
 
 
-def layer(x, w, i, spec, eps, mult):
+def layer(x, w, i, spec, eps, mult, margins=None):
     p = f"l{i}."
     h = token_shift(rms_norm(x, w[p + "norm1"], eps), w[p + "shift"])
     x = x + mult * rms_norm(mixer(h, w, p + "mix.", spec["mixer"], eps), w[p + "norm1b"], eps)
     if spec.get("mlp"):
-        y = feed_forward(rms_norm(x, w[p + "norm2"], eps), w, p + "mlp.", spec["mlp"])
+        y = feed_forward(rms_norm(x, w[p + "norm2"], eps), w, p + "mlp.", spec["mlp"], margins)
         x = x + mult * rms_norm(y, w[p + "norm2b"], eps)
     return x
 
 
-def forward(config, w, tokens, streams=None):
-    """Logits [T, vocab] of one sequence; ``streams`` (a list) receives the stream after every layer run."""
-    eps, mult = config["norm"]["eps"], config["residual_mult"]
-    x = w["embed"].astype(F64)[np.asarray(tokens)] * config["embedding"]["scale"]
+def forward(config, w, tokens, streams=None, margins=None):
+    """Logits [T, vocab] of one sequence; ``streams`` (a list) receives the stream after every layer run; ``margins``
+    (an array [T] that starts at infinity) the smallest lead of any routing decision made for each token."""
+    eps, mult = config["norm"]["eps"], config.get("residual_mult", 1.0)
+    x = w["embed"].astype(F64)[np.asarray(tokens)] * (config.get("embedding") or {}).get("scale", 1.0)
     for i, begins in layer_order(config):
         if begins is not None:
             x = x + w["loop.step"].astype(F64)[begins]
-        x = layer(x, w, i, config["layers"][i], eps, mult)
+        x = layer(x, w, i, config["layers"][i], eps, mult, margins)
         if streams is not None:
             streams.append(x.copy())
     return rms_norm(x, w["final.norm"], eps) @ w["head"].T.astype(F64)

@@ -240,12 +240,12 @@ class GroupedQueryAttention:
         else:
             linear(attended, self.w_o, accumulate_into=residual)
 
-    def mix(self, h, ctx, store, owns_cache=True, out=None):
+    def mix(self, h, ctx, store, owns_cache=True, out=None, leave_bias=False):
         """The mixer's result, float32 [T, width], for a caller that does something else with it than adding it
-        (written into ``out`` where that is given)."""
+        (written into ``out`` where that is given).  ``leave_bias``: the caller adds ``o_bias`` itself."""
         ctx.then_norm = None
         y = linear(self.attended(h, ctx, store, owns_cache), self.w_o, out_dtype=torch.float32, out=out)
-        if self.o_bias is not None:
+        if self.o_bias is not None and not leave_bias:
             ops.add_row(y, self.o_bias)
         return y
 

@@ -58,8 +58,15 @@ class SideBySideMixer:
             self.branches.append(branch_cls(branch_params, own, dtype, device))
             if self.combine != "weighted":
                 self.out_weights.append(weights[f"{name}.out"].to(torch.float32).contiguous())
+        self.bias = None
         if self.combine == "weighted":
-            self.scales = torch.tensor([float(b["scale"]) for b in params["branches"]], dtype=torch.float32, device=device)
+            factors = [float(b["scale"]) for b in params["branches"]]
+            self.scales = torch.tensor(factors, dtype=torch.float32, device=device)
+            # a bias of a branch's last product is left for whoever adds the parts up: one row, sum_b scale_b * bias_b
+            for branch, factor in zip(self.branches, factors):
+                if getattr(branch, "o_bias", None) is not None:
+                    row = branch.o_bias.to(torch.float32) * factor
+                    self.bias = row if self.bias is None else self.bias + row
         if not self.branches:
             raise ConfigError("a side-by-side mixer needs at least one branch")
         self.graph_safe = all(getattr(b, "graph_safe", False) for b in self.branches)
@@ -75,14 +82,19 @@ class SideBySideMixer:
         ctx.then_norm = None
         parts = torch.empty((len(self.branches), h.shape[0], self.width), dtype=torch.float32, device=h.device)
         for i, (branch, branch_store) in enumerate(zip(self.branches, store)):
-            branch.mix(h, ctx, branch_store, owns_cache, out=parts[i])
-        return WeightedParts(parts, self.scales)
+            if getattr(branch, "o_bias", None) is not None:
+                branch.mix(h, ctx, branch_store, owns_cache, out=parts[i], leave_bias=True)
+            else:
+                branch.mix(h, ctx, branch_store, owns_cache, out=parts[i])
+        return WeightedParts(parts, self.scales, self.bias)
 
     def forward(self, h, residual, ctx, store, owns_cache=True):
         ctx.then_norm = None
         if self.combine == "weighted":
             y = self.mix(h, ctx, store, owns_cache)
             ops.add_scaled_parts(residual, y.parts, y.scales)
+            if y.bias is not None:
+                ops.add_row(residual, y.bias)
             return
         share = 1.0 / len(self.branches)
         for branch, weight, branch_store in zip(self.branches, self.out_weights, store):
