@@ -288,6 +288,29 @@ def test_the_gates_activation_may_be_the_tanh_gelu():
     _close(out.cpu().numpy(), plain.silu(gate_up[:, :20]) * gate_up[:, 20:], 2e-6)
 
 
+@pytest.mark.parametrize("rows", [1, 8, 40, 128, 300])
+def test_the_products_that_end_in_a_gate_take_the_tanh_gelu_too(rows):
+    """The few-row and the tiled bfloat16 products with the gate in their last step (1 to 16 rows, up to 128 rows, and
+    more), through the feed-forward part that picks among them."""
+    from xeno_rt_b200.core import parse_dtype
+    from xeno_rt_b200.parts import StepContext, part_class
+    rng = np.random.default_rng(rows)
+    d, inner = 256, 640
+    rnd = lambda *shape: torch.tensor(rng.normal(0, 1.5 / np.sqrt(shape[-1]), shape), dtype=torch.float32).to(torch.bfloat16).to(DEV)
+    w = {"gate": rnd(inner, d), "up": rnd(inner, d), "down": rnd(d, inner)}
+    part = part_class("feed_forward", "swiglu")({"width": d, "inner": inner, "activation": "gelu_tanh"}, w, parse_dtype("bfloat16"), DEV)
+    h = torch.tensor(rng.normal(size=(rows, d)), dtype=torch.float32).to(torch.bfloat16).to(DEV)
+    ctx = StepContext(n_tokens=rows, n_seqs=1, token_ids=None, tok_pos=None, tok_slot=None, cu_seqlens=None, seq_slot=None,
+                      seq_start=None, new_lens=[rows], starts=[0], all_single=False, max_new=rows, max_context=rows,
+                      dtype=parse_dtype("bfloat16"))
+    got = part.apply(h, ctx).cpu().numpy()
+    pw = {"m." + k: v.float().cpu().numpy().astype(np.float64) for k, v in w.items()}
+    want = plain.gated(h.float().cpu().numpy().astype(np.float64), pw, "m.", plain.gelu_tanh)
+    other = plain.gated(h.float().cpu().numpy().astype(np.float64), pw, "m.", plain.silu)
+    _close(got, want, 1.5e-2)
+    assert np.abs(other - want).max() > 0.1 * np.abs(want).max()    # the silu gate would be another answer
+
+
 # ------------------------------------------------------------------------------------------------ small steps
 @pytest.mark.parametrize("width", [36, 192, 1500])
 def test_the_norm_after_a_sublayer_takes_factors_a_bias_and_a_second_norm(width):

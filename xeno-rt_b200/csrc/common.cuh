@@ -53,7 +53,15 @@ struct RowScale {
   int parts = 0;
   int width = 1;
   float eps = 0.f;
+  int gate_act = 0;                 // of a gated product (mode 2): 0 silu, 1 the tanh form of gelu
 };
+
+// The launchers take the gate's activation in the bits of `mode` above the low four: mode 2 | (act << 4).
+inline bool split_gate_act(int& mode, RowScale& scale) {
+  scale.gate_act = mode >> 4;
+  mode &= 15;
+  return scale.gate_act == 0 || (scale.gate_act == 1 && mode == 2);
+}
 
 // What an attention layer may do to its scores beside the scale, the causal bound and the window (0 = off):
 // keys [0, keep_first) stay visible behind a window; s <- softcap * tanh(s / softcap); then
@@ -73,6 +81,11 @@ template <typename T> __device__ __forceinline__ T from_float(float v);
 template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
   return __float2bfloat16_rn(v);
+}
+
+// The gate of a gated feed-forward: silu, or (act 1) 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))).
+__device__ __forceinline__ float gelu_tanh_gate(float g) {
+  return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

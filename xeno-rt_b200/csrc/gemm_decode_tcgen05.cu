@@ -62,6 +62,10 @@ __host__ __device__ inline int dg_rows_per_block(int splits) { return ((DG_ROWS 
 // what an epilogue that runs once a block pays for (its code comes cold from the L2).
 template <typename TO> __device__ __forceinline__ float silu_for(float x) { return x / (1.0f + expf(-x)); }
 template <> __device__ __forceinline__ float silu_for<__nv_bfloat16>(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+// the gate of a gated product: silu, or (act 1) the tanh form of gelu
+template <typename TO> __device__ __forceinline__ float gate_for(float x, int act) {
+  return act == 1 ? gelu_tanh_gate(x) : silu_for<TO>(x);
+}
 
 __device__ __forceinline__ void store_four(float* dst, const float (&v)[4]) {
   *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
@@ -305,7 +309,7 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
             for (int j = 0; j < 16; ++j) {
               const float inv = scaled ? row_inv[c + j] : 1.f;
               val[j] = __uint_as_float(v[j]) * inv;
-              if (MODE == 2) val[j] = silu_for<TO>(val[j]) * (__uint_as_float(u[j]) * inv);
+              if (MODE == 2) val[j] = gate_for<TO>(val[j], scale.gate_act) * (__uint_as_float(u[j]) * inv);
               if (MODE == 1) val[j] += old[j];
             }
 #pragma unroll
@@ -399,7 +403,7 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
               for (int j = 0; j < 16; ++j) {
                 const float inv = scaled ? row_inv[m0 + j] : 1.f;
                 val[j] = sums[0][j] * inv;
-                if (MODE == 2) val[j] = silu_for<TO>(val[j]) * (sums[GROUPS - 1][j] * inv);
+                if (MODE == 2) val[j] = gate_for<TO>(val[j], scale.gate_act) * (sums[GROUPS - 1][j] * inv);
                 if (MODE == 1) val[j] += old[j];
               }
 #pragma unroll
@@ -478,7 +482,7 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
               const float4 up = sums[u][GROUPS - 1];
               const float ups[4] = {up.x * inv, up.y * inv, up.z * inv, up.w * inv};
 #pragma unroll
-              for (int j = 0; j < 4; ++j) val[j] = silu_for<TO>(val[j]) * ups[j];
+              for (int j = 0; j < 4; ++j) val[j] = gate_for<TO>(val[j], scale.gate_act) * ups[j];
             }
             if (MODE == 1) { val[0] += old[u].x; val[1] += old[u].y; val[2] += old[u].z; val[3] += old[u].w; }
             store_four(out + (size_t)m_of[u] * shape.ldo + n_of[u], val);
@@ -531,7 +535,7 @@ gemm_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
             sums[gr] = t;
           }
           float val = sums[0] * inv;
-          if (MODE == 2) val = (val / (1.0f + expf(-val))) * (sums[GROUPS - 1] * inv);
+          if (MODE == 2) val = (scale.gate_act == 1 ? gelu_tanh_gate(val) : val / (1.0f + expf(-val))) * (sums[GROUPS - 1] * inv);
           TO* dst = out + (size_t)m * shape.ldo + n;
           if (MODE == 1) *dst = from_float<TO>(*reinterpret_cast<const float*>(dst) + val);
           else *dst = from_float<TO>(val);
@@ -817,8 +821,9 @@ XRT_EXPORT int xrt_gemm_decode_tcgen05_normed(void* out, const void* x, const vo
                                               int M, int N, int K, int ldx, int ldo, int w_rows, int out_dtype, int mode,
                                               int up_rows, int sm_count, int* error_flag, const float* squares,
                                               int square_parts, float eps, cudaStream_t stream) {
-  if (squares != nullptr && (square_parts <= 0 || mode == 1)) return XRT_ERR_ARGUMENT;
   xrt::RowScale scale;
+  if (mode < 0 || !xrt::split_gate_act(mode, scale)) return XRT_ERR_ARGUMENT;
+  if (squares != nullptr && (square_parts <= 0 || mode == 1)) return XRT_ERR_ARGUMENT;
   scale.squares = squares; scale.parts = square_parts; scale.width = K; scale.eps = eps;
   return xrt::decode_gemm(out, x, w, partial, counters, M, N, K, ldx, ldo, w_rows, out_dtype, mode, up_rows, sm_count,
                           error_flag, scale, xrt::NormEmit(), stream);

@@ -224,7 +224,9 @@ gemm_stream_kernel(TO* __restrict__ out, const __nv_bfloat16* __restrict__ x, co
       const float inv = (MODE != 1 && scale.squares != nullptr) ? row_inv[m] : 1.f;
       const float first = total(rg) * inv;
       TO* dst = out + (size_t)m * ldo + row;
-      if (MODE == 2) *dst = from_float<TO>((first / (1.0f + expf(-first))) * (total(ROW_GROUPS + rg) * inv));
+      if (MODE == 2)
+        *dst = from_float<TO>((scale.gate_act == 1 ? gelu_tanh_gate(first) : first / (1.0f + expf(-first))) *
+                              (total(ROW_GROUPS + rg) * inv));
       else if (MODE == 1) {
         const float updated = to_float(*dst) + first;
         *dst = from_float<TO>(updated);
@@ -350,8 +352,9 @@ XRT_EXPORT int xrt_gemm_stream_normed(void* out, const void* x, const void* w, i
                                       int out_dtype, int mode, int up_rows, void* scaled, int ld_scaled,
                                       const void* norm_weight, int norm_dtype, float* squares, const float* in_squares,
                                       int in_parts, float eps, cudaStream_t stream) {
-  if (in_squares != nullptr && (in_parts <= 0 || mode == 1)) return XRT_ERR_ARGUMENT;
   xrt::RowScale scale;
+  if (mode < 0 || !xrt::split_gate_act(mode, scale)) return XRT_ERR_ARGUMENT;
+  if (in_squares != nullptr && (in_parts <= 0 || mode == 1)) return XRT_ERR_ARGUMENT;
   scale.squares = in_squares; scale.parts = in_parts; scale.width = K; scale.eps = eps;
   if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldo < N || mode < 0 || mode > 2) return XRT_ERR_ARGUMENT;
   if (mode == 1 && out_dtype != XRT_F32) return XRT_ERR_ARGUMENT;

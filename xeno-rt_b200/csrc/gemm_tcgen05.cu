@@ -210,7 +210,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const float g = __uint_as_float(v[j]) * row_inv;
-            v[j] = __float_as_uint((g / (1.0f + expf(-g))) * (__uint_as_float(u[j]) * row_inv));
+            const float a = scale.gate_act == 1 ? gelu_tanh_gate(g) : g / (1.0f + expf(-g));
+            v[j] = __float_as_uint(a * (__uint_as_float(u[j]) * row_inv));
           }
         } else {
           tmem_wait_ld();
@@ -368,13 +369,14 @@ XRT_EXPORT int xrt_gemm_tcgen05_normed(void* out, const void* x, const void* w, 
                                        int w_rows, int out_dtype, int mode, int up_rows, int* error_flag, void* scaled,
                                        int ld_scaled, const void* norm_weight, int norm_dtype, float* squares,
                                        const float* in_squares, int in_parts, float eps, cudaStream_t stream) {
+  xrt::RowScale scale;
+  if (mode < 0 || !xrt::split_gate_act(mode, scale)) return XRT_ERR_ARGUMENT;
   if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldo < N || mode < 0 || mode > 2) return XRT_ERR_ARGUMENT;
   if (mode == 1 && out_dtype != XRT_F32) return XRT_ERR_ARGUMENT;
   if (mode == 2 ? w_rows < up_rows + N : w_rows < N) return XRT_ERR_ARGUMENT;
   if (out_dtype != XRT_F32 && out_dtype != XRT_BF16) return XRT_ERR_UNSUPPORTED;
   if (K % 8 != 0 || ldx % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return XRT_ERR_UNSUPPORTED;
   xrt::NormEmit emit;
-  xrt::RowScale scale;
   if (scaled != nullptr) {
     if (mode != 1 || norm_weight == nullptr || squares == nullptr || ld_scaled < N) return XRT_ERR_ARGUMENT;
     if (N % 4 != 0 || ldo % 4 != 0 || ld_scaled % 4 != 0 || (norm_dtype != XRT_F32 && norm_dtype != XRT_BF16) ||

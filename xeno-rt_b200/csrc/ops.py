@@ -291,6 +291,13 @@ def layernorm(out, x, weight, eps: float, rows=None) -> None:
 GATE_ACTS = {"silu": 0, "gelu_tanh": 1}
 
 
+def _gate_code(act: str, mode: str) -> int:
+    """The number of a gated product's activation ("swiglu" mode only: silu, or the tanh form of gelu)."""
+    if act not in GATE_ACTS or (act != "silu" and mode != "swiglu"):
+        raise KernelError(f"the gate's activation {act!r} is not one of {sorted(GATE_ACTS)}, or the product has no gate")
+    return GATE_ACTS[act]
+
+
 def swiglu(out, gate_up, act: str = "silu") -> None:
     """out[t, f] = act(gate_up[t, f]) * gate_up[t, F + f]; ``act`` "silu" or "gelu_tanh" (the tanh form of gelu)."""
     if act not in GATE_ACTS:
@@ -465,7 +472,8 @@ def gemm_decode_tcgen05_norm_parts(m: int, n: int, k: int, device) -> int:
     return _decode_norm_parts[key]
 
 
-def gemm_decode_tcgen05(out, x, w, mode: str = "store", up_rows: int = 0, squares=None, eps: float = 0.0, norm=None) -> None:
+def gemm_decode_tcgen05(out, x, w, mode: str = "store", up_rows: int = 0, squares=None, eps: float = 0.0, norm=None,
+                        gate_act: str = "silu") -> None:
     """bfloat16 product for at most 128 rows on the tcgen05 tensor cores with swapped operands:
     the weight is streamed once by TMA, K is split across blocks and summed in split order.
     ``squares`` (float32 [parts, rows], from a product with ``norm=...``): ``x`` is a residual times
@@ -484,6 +492,7 @@ def gemm_decode_tcgen05(out, x, w, mode: str = "store", up_rows: int = 0, square
     if (n + 127) // 128 > _COUNTER_SLOTS:
         raise KernelError("gemm_decode_tcgen05: more tiles than counters")
     code = {"store": 0, "accumulate": 1, "swiglu": 2}[mode]
+    coded = code | (_gate_code(gate_act, mode) << 4)  # the gate's activation rides above the mode's four bits
     flag, counters, sms = device_state(x.device)
     lib = library()
     floats = lib.xrt_gemm_decode_tcgen05_scratch(m, n, k, code, sms)
@@ -504,7 +513,7 @@ def gemm_decode_tcgen05(out, x, w, mode: str = "store", up_rows: int = 0, square
         return
     _check(lib.xrt_gemm_decode_tcgen05_normed(
         out.data_ptr(), x.data_ptr(), _ptr(w, "w"), _ptr(partial, "partial"), counters.data_ptr(), m, n, k, x.stride(0),
-        out.stride(0), w.shape[0], _code(out.dtype), code, up_rows, sms, flag.data_ptr(),
+        out.stride(0), w.shape[0], _code(out.dtype), coded, up_rows, sms, flag.data_ptr(),
         _ptr(squares, "squares", torch.float32), 0 if squares is None else squares.shape[0], float(eps), _stream()),
         "gemm_decode_tcgen05")
 
@@ -514,7 +523,8 @@ def gemm_tcgen05_norm_parts(n: int) -> int:
     return library().xrt_gemm_tcgen05_norm_parts(int(n))
 
 
-def gemm_tcgen05(out, x, w, mode: str = "store", up_rows: int = 0, norm=None, squares=None, eps: float = 0.0) -> None:
+def gemm_tcgen05(out, x, w, mode: str = "store", up_rows: int = 0, norm=None, squares=None, eps: float = 0.0,
+                 gate_act: str = "silu") -> None:
     """bfloat16 product for many rows on the tcgen05 tensor cores with TMA-fed operands; modes as
     for ``gemm_stream``.  ``norm`` = (scaled, weight, squares) with "accumulate": the product prepares the
     RMSNorm that follows it (as ``gemm_stream`` does; ``squares`` is float32 [gemm_tcgen05_norm_parts(n), m]).
@@ -529,6 +539,7 @@ def gemm_tcgen05(out, x, w, mode: str = "store", up_rows: int = 0, norm=None, sq
     if x.stride(1) != 1 or out.stride(1) != 1 or not x.is_cuda or not out.is_cuda:
         raise KernelError("gemm_tcgen05: rows must be contiguous and on a CUDA device")
     code = {"store": 0, "accumulate": 1, "swiglu": 2}[mode]
+    coded = code | (_gate_code(gate_act, mode) << 4)  # the gate's activation rides above the mode's four bits
     flag = error_flag(x.device)
     scaled = weight = emitted = None
     if norm is not None:
@@ -539,7 +550,7 @@ def gemm_tcgen05(out, x, w, mode: str = "store", up_rows: int = 0, norm=None, sq
     if squares is not None and (mode == "accumulate" or squares.dim() != 2 or squares.shape[1] != m):
         raise KernelError("gemm_tcgen05: squares must be [parts, rows], and not with accumulate")
     _check(_kernels().xrt_gemm_tcgen05_normed(
-        out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0), out.stride(0), w.shape[0], _code(out.dtype), code,
+        out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0), out.stride(0), w.shape[0], _code(out.dtype), coded,
         up_rows, flag.data_ptr(), _ptr(scaled, "scaled", torch.bfloat16), 0 if scaled is None else scaled.stride(0),
         _ptr(weight, "weight"), _code(weight.dtype) if weight is not None else 0, _ptr(emitted, "squares", torch.float32),
         _ptr(squares, "squares", torch.float32), 0 if squares is None else squares.shape[0], float(eps), _stream()),
@@ -557,7 +568,8 @@ def gemm_stream_norm_parts(m: int, n: int) -> int:
     return parts
 
 
-def gemm_stream(out, x, w, mode: str = "store", up_rows: int = 0, norm=None, squares=None, eps: float = 0.0) -> None:
+def gemm_stream(out, x, w, mode: str = "store", up_rows: int = 0, norm=None, squares=None, eps: float = 0.0,
+                gate_act: str = "silu") -> None:
     """bfloat16 product for at most 64 rows that streams the weight once; ``mode`` is "store",
     "accumulate" (into a float32 out) or "swiglu" (out[m, n] = silu(x . w[n]) * (x . w[n + up_rows])).
     ``norm`` = (scaled, weight, squares) with "accumulate" and at most 16 rows: the product also
@@ -575,23 +587,24 @@ def gemm_stream(out, x, w, mode: str = "store", up_rows: int = 0, norm=None, squ
     if x.stride(1) != 1 or out.stride(1) != 1 or not x.is_cuda or not out.is_cuda:
         raise KernelError("gemm_stream: rows must be contiguous and on a CUDA device")
     code = {"store": 0, "accumulate": 1, "swiglu": 2}[mode]
+    coded = code | (_gate_code(gate_act, mode) << 4)  # the gate's activation rides above the mode's four bits
     if squares is not None:
         if norm is not None or mode == "accumulate" or squares.dim() != 2 or squares.shape[1] != m or not squares.is_contiguous():
             raise KernelError("gemm_stream: squares must be [parts, rows], and not with accumulate or a following norm")
         _check(_kernels().xrt_gemm_stream_normed(
-            out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0), out.stride(0), _code(out.dtype), code, up_rows,
+            out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0), out.stride(0), _code(out.dtype), coded, up_rows,
             0, 0, 0, 0, 0, _ptr(squares, "squares", torch.float32), squares.shape[0], float(eps), _stream()), "gemm_stream")
         return
     if norm is None:
         _check(_kernels().xrt_gemm_stream(out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0), out.stride(0),
-                                         _code(out.dtype), code, up_rows, _stream()), "gemm_stream")
+                                         _code(out.dtype), coded, up_rows, _stream()), "gemm_stream")
         return
     scaled, weight, squares = norm
     if (mode != "accumulate" or scaled.shape != (m, n) or scaled.stride(1) != 1 or weight.numel() != n
             or tuple(squares.shape) != (gemm_stream_norm_parts(m, n), m)):
         raise KernelError("gemm_stream: the buffers of the following norm do not fit the product")
     _check(_kernels().xrt_gemm_stream_norm(
-        out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0), out.stride(0), _code(out.dtype), code, up_rows,
+        out.data_ptr(), x.data_ptr(), _ptr(w, "w"), m, n, k, x.stride(0), out.stride(0), _code(out.dtype), coded, up_rows,
         _ptr(scaled, "scaled", torch.bfloat16), scaled.stride(0), _ptr(weight, "weight"), _code(weight.dtype),
         _ptr(squares, "squares", torch.float32), _stream()), "gemm_stream")
 

@@ -51,9 +51,9 @@ class SwiGLUFeedForward:
     def _act(self, h):
         act = torch.empty((h.shape[0], self.inner), dtype=self.act_dtype, device=h.device)
         fused = False
-        if self.act_dtype == torch.bfloat16 and h.dtype == torch.bfloat16 and self.activation == "silu":
+        if self.act_dtype == torch.bfloat16 and h.dtype == torch.bfloat16:
             from . import linear_bf16
-            fused = linear_bf16.run_swiglu(act, h, self.w_gate_up, self.inner)
+            fused = linear_bf16.run_swiglu(act, h, self.w_gate_up, self.inner, self.activation)
         if not fused:
             gate_up = linear(h, self.w_gate_up, out_dtype=torch.float32)
             ops.swiglu(act, gate_up, self.activation)

@@ -72,14 +72,14 @@ def _decode_kernel(rows: int, n: int, k: int, mode: str, device) -> str:
     return "tcgen05" if tcgen05_for_few_rows(sms, rows, n, k, mode) else "stream"
 
 
-def _product(out, x, weight, mode: str, up_rows: int = 0) -> None:
+def _product(out, x, weight, mode: str, up_rows: int = 0, gate_act: str = "silu") -> None:
     rows = x.shape[0]
     if rows > ops.DECODE_TCGEN05_MAX_ROWS:
-        ops.gemm_tcgen05(out, x, weight, mode, up_rows)
+        ops.gemm_tcgen05(out, x, weight, mode, up_rows, gate_act=gate_act)
     elif _decode_kernel(rows, out.shape[1], x.shape[1], mode, x.device) == "stream":
-        ops.gemm_stream(out, x, weight, mode, up_rows)
+        ops.gemm_stream(out, x, weight, mode, up_rows, gate_act=gate_act)
     else:
-        ops.gemm_decode_tcgen05(out, x, weight, mode, up_rows)
+        ops.gemm_decode_tcgen05(out, x, weight, mode, up_rows, gate_act=gate_act)
 
 
 def takes_pending(rows: int, n: int, k: int, mode: str, device) -> bool:
@@ -149,14 +149,16 @@ def run(out, x, weight, accumulate: bool) -> bool:
     return True
 
 
-def run_swiglu(out, x, weight_gate_up, inner: int) -> bool:
-    """out = silu(x . gate^T) * (x . up^T) for the fused weight [2 * inner, width]; False if no
-    fused kernel takes the shape."""
+def run_swiglu(out, x, weight_gate_up, inner: int, gate_act: str = "silu") -> bool:
+    """out = act(x . gate^T) * (x . up^T) for the fused weight [2 * inner, width], act = silu or ``gate_act``
+    "gelu_tanh"; False if no fused kernel takes the shape."""
     from .norm import PendingNorm
     if isinstance(x, PendingNorm):
+        if gate_act != "silu":
+            return False
         run_pending(out, x, weight_gate_up, inner)
         return True
     if not aligned(x, weight_gate_up):
         return False
-    _product(out, x, weight_gate_up, "swiglu", inner)
+    _product(out, x, weight_gate_up, "swiglu", inner, gate_act)
     return True
