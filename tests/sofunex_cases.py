@@ -207,22 +207,22 @@ def random_config(rng) -> dict:
     """A configuration drawn at random: any order of layers, any of the sizes and options the cases above use and
     more."""
     pick = lambda *values: values[int(rng.integers(len(values)))]
-    width = pick(32, 36, 64, 96, 128, 200)
+    width = pick(32, 36, 64, 96, 128, 200, 320)
     layers = []
     for _ in range(int(rng.integers(1, 6))):
-        kv = pick(1, 2, 3)
-        dim = pick(8, 12, 16, 24, 32, 48, 64, 128)
-        rot = pick(None, *[(r, pick(100.0, 10000.0, 5e5)) for r in (2, 4, 8, 12, 16, 24, 32, 64, 128) if r <= dim])
-        l = left(kv * pick(1, 2, 3, 4, 8), kv, dim, pick(8, 16, 20, 24, 40, 64, 128), float(pick(0.5, 1.0, 2.0, 4.0)) / np.sqrt(dim),
+        kv = pick(1, 2, 3, 4)
+        dim = pick(8, 12, 16, 24, 32, 48, 64, 72, 96, 128)
+        rot = pick(None, *[(r, pick(100.0, 10000.0, 5e5)) for r in (2, 4, 8, 12, 16, 24, 32, 64, 96, 128) if r <= dim])
+        l = left(kv * pick(1, 2, 3, 4, 6, 8, 12), kv, dim, pick(8, 16, 20, 24, 40, 64, 96, 128), float(pick(0.5, 1.0, 2.0, 4.0)) / np.sqrt(dim),
                  conv=pick(None, 1, 2, 3, 4, 5), rot=rot, factor=pick(None, 1.0, 2.0, 8.0) if rot else None,
-                 size=pick(None, 1, 5, 33, 64, 70, 130, 400))
-        r = right(pick(1, 2, 3, 4), pick(8, 12, 16, 20, 32, 48, 64), pick(4, 5, 8, 16, 24))
+                 size=pick(None, 1, 5, 33, 64, 70, 72, 130, 400))
+        r = right(pick(1, 2, 3, 4, 6), pick(8, 12, 16, 20, 32, 48, 64, 96, 128), pick(4, 5, 8, 16, 24, 32))
         m = mixer(l, r, pick(1.0, 0.6, 1.4), pick(1.0, 0.9, 0.3))
         kind = pick("dense", "moe", "moe", None)
         if kind == "dense":
             mlp = dense(pick(24, 52, 96, 160))
         elif kind == "moe":
-            count = pick(1, 2, 4)
+            count = pick(1, 2, 4, 8)
             size = pick(1, 2, 3, 4, 10)
             keep = pick(*range(1, count + 1))
             mlp = moe(count * size, pick(*[t for t in (1, 2, 3, keep * size) if t <= keep * size]), pick(8, 12, 32, 64),
@@ -237,5 +237,5 @@ def random_config(rng) -> dict:
     if rng.random() < 0.7:
         start = int(rng.integers(0, len(layers)))
         stop = int(rng.integers(start + 1, len(layers) + 1))
-        config["loop"] = {"start": start, "stop": stop, "times": pick(1, 2, 3)}
+        config["loop"] = {"start": start, "stop": stop, "times": pick(1, 2, 3, 4)}
     return config
