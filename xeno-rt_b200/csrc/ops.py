@@ -883,7 +883,7 @@ def short_conv(out, x, weight, state, cu_seqlens, seq_slot, max_new: int, act: s
                                     _ptr(state if taps > 1 else None, "state", torch.float32),
                                     _ptr(cu_seqlens, "cu_seqlens", torch.int32), _ptr(seq_slot, "seq_slot", torch.int32),
                                     n_seqs, int(max_new), channels, taps, _ACTS[act], _stream()), "short_conv")
-    if taps > 1:
+    if taps > 1 and int(max_new) != 1:  # longer portions leave the state in a second launch
         add_launches(1)
 
 

@@ -353,6 +353,41 @@ __global__ void short_conv_state_kernel(float* __restrict__ state, const float* 
   }
 }
 
+// A step whose sequences bring one token each: output and new state in one launch.  A thread has one channel of one
+// sequence, so what it reads of the state it writes itself; the taps are walked in the order of the kernel above
+// (the state's entries, then the new input), which gives the same bits.
+template <int MAX_KEEP>
+__global__ void short_conv_single_kernel(float* __restrict__ out, const float* __restrict__ x, int x_stride,
+                                         const float* __restrict__ w, const float* __restrict__ bias,
+                                         const float* __restrict__ in_bias, float* __restrict__ state,
+                                         const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
+                                         int channels, int taps, int act) {
+  pdl_trigger();
+  pdl_wait();
+  const int s = blockIdx.x;
+  const int slot = seq_slot[s];
+  const int begin = cu_seqlens[s], len = cu_seqlens[s + 1] - begin;
+  if (slot < 0 || len <= 0) return;
+  const int keep = taps - 1;
+  float* st = state + (size_t)slot * keep * channels;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
+    const float xv = x[(size_t)begin * x_stride + c] + (in_bias != nullptr ? in_bias[c] : 0.f);
+    float acc = bias != nullptr ? bias[c] : 0.f;
+    float old[MAX_KEEP];
+#pragma unroll
+    for (int i = 0; i < MAX_KEEP; ++i)
+      if (i < keep) {
+        old[i] = st[(size_t)i * channels + c];
+        acc = fmaf(w[c * taps + i], old[i], acc);
+      }
+    acc = fmaf(w[c * taps + keep], xv, acc);
+    out[(size_t)begin * channels + c] = activate(acc, act);
+#pragma unroll
+    for (int i = 0; i < MAX_KEEP; ++i)
+      if (i < keep) st[(size_t)i * channels + c] = i + 1 < keep ? old[i + 1] : xv;
+  }
+}
+
 // ------------------------------------------------------------------------------------------ small steps
 // mode 0: a = sigmoid(z + bias)^(1 / tau) = exp(-softplus(-(z + bias)) / tau)
 // mode 1: a = exp(-exp(a_log[head]) * softplus(z + bias))
@@ -616,6 +651,12 @@ XRT_EXPORT int xrt_short_conv(float* out, const float* x, int x_stride, const fl
   const int tile_tokens = 8;
   const int threads = channels >= 128 ? 128 : 64;
   const int channel_blocks = (channels + threads - 1) / threads;
+  if (max_new == 1 && taps > 1) {  // single tokens: one launch
+    xrt::launch_kernel(xrt::short_conv_single_kernel<8>, dim3(n_seqs, channel_blocks < 65535 ? channel_blocks : 65535),
+                       dim3(threads), 0, stream, out, x, x_stride, w, bias, in_bias, state, cu_seqlens, seq_slot, channels,
+                       taps, act);
+    return xrt::launch_status();
+  }
   xrt::launch_kernel(xrt::short_conv_kernel,
                      dim3(n_seqs, (max_new + tile_tokens - 1) / tile_tokens, channel_blocks < 65535 ? channel_blocks : 65535),
                      dim3(threads), 0, stream, out, x, x_stride, w, bias, in_bias, (const float*)state, cu_seqlens, seq_slot, channels, taps, tile_tokens,
