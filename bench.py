@@ -360,19 +360,19 @@ def zogevik_config(width: int, heads: int, kv_heads: int, head_dim: int, inner: 
 def sofunex_config(width: int, heads: int, kv_heads: int, head_dim: int, inner: int, layers: int, vocab: int) -> dict:
     """A Sofunex model at the sizes of a dense decoder of that width: every layer has the side-by-side mixer
     (attention of ``heads`` x ``head_dim`` with ``kv_heads`` kv heads, 4 taps on q, k and v, a rotation over half of the
-    head with frequencies divided by 8 and a window of 1,024 keys; a delta rule of ``heads`` heads of ``head_dim`` with a
+    head with frequencies divided by 4 and a window of 1,024 keys; a delta rule of ``heads`` heads of ``head_dim`` with a
     decay product of rank 64) behind a token shift; layers alternate between a dense feed-forward of ``inner`` and 16
     experts of ``inner`` / 8 units in 4 groups of which 2 are kept, 2 a token, with a shared expert of ``inner`` / 8;
     the whole stack is one loop that runs once (so that the step which begins a pass is in the timing)."""
     mixer = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
-                      "conv": 4, "rot": {"dims": head_dim // 2, "base": 500000.0, "scaling": {"factor": 8.0}},
+                      "conv": 4, "rot": {"dims": head_dim // 2, "base": 500000.0, "scaling": {"factor": 4.0}},
                       "mask": {"size": 1024}},
-             "right": {"heads": heads, "dim": head_dim, "decay_rank": 64}, "left_scale": 0.6, "right_scale": 0.9}
+             "right": {"heads": heads, "dim": head_dim, "decay_rank": 64}, "left_scale": 0.5, "right_scale": 1.0}
     dense = {"kind": "dense", "ff": inner}
     moe = {"kind": "moe", "expert": {"ff": inner // 8}, "shared": {"ff": inner // 8},
-           "router": {"experts": 16, "top": 2, "scale": 2.0, "groups": {"count": 4, "keep": 2}}}
-    return {"architecture": "Sofunex", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
-            "embedding": {"scale": float(width) ** 0.5}, "residual_mult": 0.7, "loop": {"start": 0, "stop": layers, "times": 1},
+           "router": {"experts": 16, "top": 2, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+    return {"architecture": "Sofunex", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "embedding": {"scale": 8.0}, "residual_mult": 0.5, "loop": {"start": 0, "stop": layers, "times": 1},
             "layers": [{"type": "parallel", "mixer": mixer, "mlp": dense if i % 2 == 0 else moe} for i in range(layers)]}
 
 

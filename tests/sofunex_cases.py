@@ -85,12 +85,12 @@ CASE_ODD = {
 # heads of 128 and a width of 256: with prompts of more than 128 tokens the tiled tensor-core products run too
 CASE_WIDE = {
     "architecture": "Sofunex", "vocab": 300, "width": 256, "norm": {"eps": 1e-5}, "embedding": {"scale": 16.0},
-    "residual_mult": 0.6, "loop": {"start": 0, "stop": 2, "times": 2},
+    "residual_mult": 0.65, "loop": {"start": 0, "stop": 2, "times": 2},
     "layers": [
-        layer(mixer(left(4, 2, 128, 128, 0.09, conv=4, rot=(64, 100000.0), factor=8.0, size=130), right(2, 128, 16), 0.6, 0.9),
-              dense(384)),
+        layer(mixer(left(4, 2, 128, 128, 0.09, conv=4, rot=(64, 100000.0), factor=6.0, size=130), right(2, 128, 16), 0.55, 0.95),
+              dense(448)),
         layer(mixer(left(8, 1, 64, 64, 0.12, conv=3, rot=(64, 10000.0), size=200), right(4, 64, 32), 1.0, 1.0),
-              moe(8, 3, 64, 2.0, groups=(2, 1), shared=64)),
+              moe(8, 3, 48, 1.8, groups=(2, 1), shared=64)),
         layer(mixer(left(2, 2, 128, 64, 0.1, conv=2, rot=(32, 10000.0), factor=2.0), right(8, 32, 8), 0.8, 0.5), None),
     ],
 }
@@ -214,10 +214,10 @@ def random_config(rng) -> dict:
         dim = pick(8, 12, 16, 24, 32, 48, 64, 72, 96, 128)
         rot = pick(None, *[(r, pick(100.0, 10000.0, 5e5)) for r in (2, 4, 8, 12, 16, 24, 32, 64, 96, 128) if r <= dim])
         l = left(kv * pick(1, 2, 3, 4, 6, 8, 12), kv, dim, pick(8, 16, 20, 24, 40, 64, 96, 128), float(pick(0.5, 1.0, 2.0, 4.0)) / np.sqrt(dim),
-                 conv=pick(None, 1, 2, 3, 4, 5), rot=rot, factor=pick(None, 1.0, 2.0, 8.0) if rot else None,
-                 size=pick(None, 1, 5, 33, 64, 70, 72, 130, 400))
+                 conv=pick(None, 1, 2, 3, 4, 5), rot=rot, factor=pick(None, 1.0, 2.0, 6.0) if rot else None,
+                 size=pick(None, 1, 5, 33, 64, 70, 80, 130, 400))
         r = right(pick(1, 2, 3, 4, 6), pick(8, 12, 16, 20, 32, 48, 64, 96, 128), pick(4, 5, 8, 16, 24, 32))
-        m = mixer(l, r, pick(1.0, 0.6, 1.4), pick(1.0, 0.9, 0.3))
+        m = mixer(l, r, pick(1.0, 0.5, 1.4), pick(1.0, 0.75, 0.3))
         kind = pick("dense", "moe", "moe", None)
         if kind == "dense":
             mlp = dense(pick(24, 52, 96, 160))
@@ -232,7 +232,7 @@ def random_config(rng) -> dict:
             mlp = None
         layers.append(layer(m, mlp))
     config = {"architecture": "Sofunex", "vocab": pick(50, 101, 256), "width": width, "norm": {"eps": pick(1e-5, 1e-6)},
-              "embedding": {"scale": pick(1.0, 4.0, float(np.sqrt(width)))}, "residual_mult": pick(1.0, 0.7, 0.5),
+              "embedding": {"scale": pick(1.0, 4.0, float(np.sqrt(width)))}, "residual_mult": pick(1.0, 0.8, 0.5),
               "layers": layers}
     if rng.random() < 0.7:
         start = int(rng.integers(0, len(layers)))

@@ -60,6 +60,35 @@ def test_a_loop_repeats_its_layers_with_a_cache_each_and_begins_every_pass_with_
     assert [p.before for p in _spec(once)[2].schedule] == [None, "loop_step_0", None, None]
 
 
+def test_what_is_not_there_means_none():
+    """No key, null and (for the taps) 0 say the same: no convolution, rotation, scaling, window, groups, shared
+    expert, feed-forward or loop; factors that are not given are 1."""
+    raw = copy.deepcopy(CASES["mixed"][0])
+    left = raw["layers"][0]["mixer"]["left"]
+    left.update({"conv": 0, "rot": None, "mask": None})
+    raw["layers"][3]["mixer"]["left"]["rot"]["scaling"] = None
+    raw["layers"][1]["mlp"].update({"shared": None})
+    raw["layers"][1]["mlp"]["router"]["groups"] = None
+    raw["layers"][0]["mlp"] = None
+    raw["loop"] = None
+    for key in ("left_scale", "right_scale"):
+        raw["layers"][2]["mixer"].pop(key)
+    raw.pop("embedding")
+    raw.pop("residual_mult")
+    spec = _spec(raw)[2]
+    attention = spec.layers[0].parts["mixer"][1].params["branches"][0]["params"]
+    assert attention["conv"] is None and attention["window"] is None and attention["position"]["kind"] == "none"
+    assert spec.layers[3].parts["mixer"][1].params["branches"][0]["params"]["position"]["params"]["divide"] == 1.0
+    experts = spec.layers[1].parts["ffn"][1].params
+    assert "shared" not in experts and (experts["groups"], experts["keep_groups"]) == (1, 1)
+    assert "ffn" not in spec.layers[0].parts and not spec.stream_parts and len(spec.schedule) == 4
+    assert [b["scale"] for b in spec.layers[2].parts["mixer"][1].params["branches"]] == [1.0, 1.0]
+    assert "gain" not in spec.layers[0].parts["mixer_post"][1].params or spec.layers[0].parts["mixer_post"][1].params["gain"] == 1.0
+    assert spec.embedding.params["scale"] == 1.0
+    names = {e.name for e in spec.expected_tensors()}
+    assert "l0.mix.left.q.conv" not in names and "loop.step" not in names and "l1.mlp.shared.up" not in names
+
+
 def test_what_a_layer_is_made_of():
     spec = _spec(CASES["mixed"][0])[2]
     first, third = spec.layers[0], spec.layers[2]
@@ -85,7 +114,7 @@ def test_every_bad_key_is_reported_in_one_error():
     raw["layers"][0]["mixer"]["left"]["kv_heads"] = 3           # 4 heads are no multiple
     raw["layers"][0]["mixer"]["left"]["mask"].pop("size")
     raw["layers"][0]["mixer"]["left"]["rot"]["dims"] = 18       # beyond the head
-    raw["layers"][0]["mixer"]["left"]["conv"] = 0
+    raw["layers"][0]["mixer"]["left"]["conv"] = -2
     raw["layers"][1]["mlp"]["router"]["groups"]["count"] = 3    # 8 experts are no multiple
     raw["layers"][1]["mixer"].pop("right")
     raw["layers"][2]["mlp"] = {"kind": "swiglu"}

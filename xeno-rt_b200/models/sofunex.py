@@ -48,7 +48,7 @@ def _check_left(problems, where, m):
     _positive(problems, where, m, "scale")
     if heads % kv:
         problems.append(f"{where}: {heads} heads are not a multiple of {kv} kv_heads")
-    if m.get("conv") is not None:
+    if m.get("conv") not in (None, 0) or isinstance(m.get("conv"), bool):  # no key, null and 0 all mean no convolution
         _positive_int(problems, where, m, "conv")
     rot = m.get("rot")
     if rot is not None:
@@ -214,7 +214,7 @@ def _left(width, eps, m, prefix):
             "divide": (rot.get("scaling") or {}).get("factor", 1.0)}}
     params = {"width": width, "n_heads": m["heads"], "n_kv_heads": m["kv_heads"], "head_dim": m["dim"],
               "v_head_dim": m["vdim"], "qk_norm": "whole", "eps": eps, "window": (m.get("mask") or {}).get("size"),
-              "scale": m["scale"], "bias": True, "o_bias": True, "conv": m.get("conv"), "v_norm": "unit",
+              "scale": m["scale"], "bias": True, "o_bias": True, "conv": m.get("conv") or None, "v_norm": "unit",
               "position": position}
     names = {"q": prefix + "q", "k": prefix + "k", "v": prefix + "v", "o": prefix + "o", "q_norm": prefix + "q.norm",
              "k_norm": prefix + "k.norm", "q_bias": prefix + "q.b", "k_bias": prefix + "k.b", "v_bias": prefix + "v.b",
