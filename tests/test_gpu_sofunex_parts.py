@@ -308,7 +308,7 @@ def test_the_products_that_end_in_a_gate_take_the_tanh_gelu_too(rows):
     want = plain.gated(h.float().cpu().numpy().astype(np.float64), pw, "m.", plain.gelu_tanh)
     other = plain.gated(h.float().cpu().numpy().astype(np.float64), pw, "m.", plain.silu)
     _close(got, want, 1.5e-2)
-    assert np.abs(other - want).max() > 0.1 * np.abs(want).max()    # the silu gate would be another answer
+    assert np.abs(other - want).max() > 0.05 * np.abs(want).max()   # the silu gate would be another answer
 
 
 # ------------------------------------------------------------------------------------------------ small steps
