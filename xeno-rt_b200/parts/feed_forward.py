@@ -135,7 +135,8 @@ class RoutedExperts:
 
     @staticmethod
     def _shared_spec(params):
-        """(role prefix, params) of the shared feed-forward, or None."""
+        """The parameters of the shared feed-forward (a ``SwiGLUFeedForward`` whose tensors are this part's
+        ``shared_*`` roles), or None."""
         if not params.get("shared"):
             return None
         return {"width": params["width"], "inner": int(params["shared"]), "activation": "silu"}
